@@ -36,6 +36,11 @@ class SubBlock:
         h = h + norm_after(y)         ``after="branch"``: a norm on the branch's output (sandwich norms)
         h = norm_after(h + y)         ``after="stream"``: a norm on the stream itself (post-norm)
 
+    With ``input_filter`` (a part of role ``filter``, e.g. a causal convolution over time) the part reads
+    ``filter(x)`` instead of x; the filter works on the normed stream in float32 and keeps what it needs of a
+    request's earlier tokens in the run's state plane.  Sub-blocks of a ``parallel`` layer whose ``norm_before``
+    are equal share one normed stream (and one record of its earlier tokens).
+
     ``role`` is the part's role in the registry: ``mixer`` (it may own cache) or ``ffn``."""
 
     role: str
@@ -43,6 +48,7 @@ class SubBlock:
     norm_before: Optional[PartSpec] = None
     norm_after: Optional[PartSpec] = None
     after: str = "branch"
+    input_filter: Optional[PartSpec] = None
 
 
 ARRANGEMENTS = ("sequential", "parallel")
@@ -58,6 +64,8 @@ class LayerSpec:
                       norm, feed-forward, add: engine_server.cpp:1530-1880)
       ``parallel``    all sub-blocks read the same stream, then every branch is added
 
+    ``branch_scale``: every branch is multiplied by it as it joins the stream (``h += branch_scale * y``), in float32.
+
     A layer may hold any number of sub-blocks, at most one of them a mixer (a run of the layer has one
     cache plane), so a layer without a feed-forward, with four norms or with post-norms is data.  The
     common case keeps its short form: ``LayerSpec(norm1, mixer, norm2, ffn)`` is the two sub-blocks
@@ -69,6 +77,7 @@ class LayerSpec:
     ffn: Optional[PartSpec] = None
     arrangement: str = "sequential"
     sub_blocks: List[SubBlock] = field(default_factory=list)
+    branch_scale: float = 1.0
 
     def __post_init__(self):
         self.arrangement = _OLD_NAMES.get(self.arrangement, self.arrangement)
@@ -91,6 +100,8 @@ class LayerSpec:
                 raise ValueError(f"a sub-block's role is 'mixer' or 'ffn', not {sb.role!r}")
             if sb.after not in ("branch", "stream"):
                 raise ValueError(f"a sub-block's norm_after applies to the 'branch' or the 'stream', not {sb.after!r}")
+            if sb.after == "stream" and sb.norm_after is not None and float(self.branch_scale) != 1.0:
+                raise ValueError("a norm on the stream has no meaning beside a branch scale")
             if sb.after == "stream" and sb.norm_after is not None and self.arrangement == "parallel":
                 raise ValueError("a norm on the stream has no meaning between parallel branches")
         if sum(sb.role == "mixer" for sb in self.sub_blocks) > 1:

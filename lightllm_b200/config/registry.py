@@ -27,7 +27,7 @@ class Architecture:
 
 _ARCHITECTURES: Dict[str, Architecture] = {}
 _PARTS: Dict[str, Dict[str, Type]] = {
-    "mixer": {}, "ffn": {}, "norm": {}, "position": {}, "embedding": {}, "head": {}, "stream": {}}
+    "mixer": {}, "ffn": {}, "norm": {}, "position": {}, "embedding": {}, "head": {}, "stream": {}, "filter": {}}
 
 
 def register_architecture(name: str, config_from_dict, build_spec, replace: bool = False,
@@ -42,8 +42,8 @@ def register_architecture(name: str, config_from_dict, build_spec, replace: bool
 
 def register_part(role: str, kind: str, cls: Type, replace: bool = False) -> None:
     """Make a part class buildable from ``PartSpec(kind=...)`` in the given role
-    (``mixer``, ``ffn``, ``norm``, ``position``, ``embedding``, ``head`` or ``stream``: a part that
-    rewrites the residual stream before a run entry)."""
+    (``mixer``, ``ffn``, ``norm``, ``position``, ``embedding``, ``head``, ``stream``: a part that
+    rewrites the residual stream before a run entry, or ``filter``: a part that rewrites what a sub-block reads)."""
     if role not in _PARTS:
         raise ValueError(f"unknown part role {role!r}; roles are {sorted(_PARTS)}")
     if kind in _PARTS[role] and not replace:

@@ -40,10 +40,24 @@ struct AttnParams {
     int max_pages, page_size, Hq, Hkv, hd, window, BQ, nsplit;
     int hdv;              // width of a value row and of an output row (hd for ordinary attention)
     const float* sinks;   // [Hq] or null: exp(sinks[h]) joins the softmax denominator once, with no key and no value
+    int v_shared;         // the value rows belong to no kv head: every query reads the whole row of hdv values of a slot
+    int out_f32;          // out is float whatever the dtype of q and the caches
     float scale;
     float* part_acc;  // [tiles, Hkv, nsplit, BQ*G, hdv]
     float* part_ml;   // [tiles, Hkv, nsplit, BQ*G, 2]
 };
+
+// One output value: float when the caller asked for it, else the dtype of q.
+template <typename T>
+__device__ __forceinline__ void store_out(const AttnParams& p, size_t i, float v) {
+    if (p.out_f32) ((float*)p.out)[i] = v;
+    else ((T*)p.out)[i] = llb_from_float<T>(v);
+}
+
+// Where the value row of a slot begins for kv head kvh.
+__device__ __forceinline__ size_t value_row(const AttnParams& p, size_t slot, int kvh) {
+    return p.v_shared ? slot * (size_t)p.hdv : (slot * p.Hkv + kvh) * (size_t)p.hdv;
+}
 
 template <typename T>
 __global__ void __launch_bounds__(NWARPS * 32) paged_attention_kernel(AttnParams p) {
@@ -106,7 +120,7 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_kernel(AttnParams
                 const int page = bt[kpos / p.page_size];
                 const size_t slot = (size_t)page * p.page_size + (kpos % p.page_size);
                 const T* kr = kc + (slot * p.Hkv + kvh) * hd;
-                const T* vr = vc + (slot * p.Hkv + kvh) * hdv;
+                const T* vr = vc + value_row(p, slot, kvh);
                 for (int d = lane; d < hd; d += 32) Ks[j * kstride + d] = llb_to_float(kr[d]);
                 for (int d = lane; d < hdv; d += 32) Vs[j * hdv + d] = llb_to_float(vr[d]);
             } else {
@@ -155,15 +169,14 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_kernel(AttnParams
     }
 
     if (p.nsplit == 1) {
-        T* out = (T*)p.out;
         for (int v = warp; v < nqv; v += NWARPS) {
             const int r = v / G, g = v - r * G;
             if (r >= nrows) continue;
             float den = Ls[v];
             if (p.sinks) den += expf(p.sinks[kvh * G + g] - Ms[v]);
             const float inv = 1.0f / den;
-            T* o = out + ((size_t)(row0 + r) * p.Hq + kvh * G + g) * hdv;
-            for (int d = lane; d < hdv; d += 32) o[d] = llb_from_float<T>(Acc[(size_t)v * hdv + d] * inv);
+            const size_t o = ((size_t)(row0 + r) * p.Hq + kvh * G + g) * hdv;
+            for (int d = lane; d < hdv; d += 32) store_out<T>(p, o + d, Acc[(size_t)v * hdv + d] * inv);
         }
     } else {
         const size_t base = (((size_t)tile * p.Hkv + kvh) * p.nsplit + split) * nqv;
@@ -193,7 +206,6 @@ __global__ void __launch_bounds__(32) attention_merge_kernel(AttnParams p) {
     const int q0 = p.tile_q0[tile];
     const int nrows = min(p.BQ, p.span_len[span] - q0);
     const int row0 = p.span_row[span] + q0;
-    T* out = (T*)p.out;
     const size_t base0 = ((size_t)tile * p.Hkv + kvh) * p.nsplit;
     for (int r = 0; r < nrows; ++r) {
         const int v = r * G + g;
@@ -216,7 +228,7 @@ __global__ void __launch_bounds__(32) attention_merge_kernel(AttnParams p) {
             float a = 0.0f;
 #pragma unroll 8
             for (int s = 0; s < p.nsplit; ++s) a = fmaf(wsm[s], p.part_acc[((base0 + s) * nqv + v) * p.hdv + d], a);
-            out[((size_t)(row0 + r) * p.Hq + head) * p.hdv + d] = llb_from_float<T>(a * inv);
+            store_out<T>(p, ((size_t)(row0 + r) * p.Hq + head) * p.hdv + d, a * inv);
         }
         __syncwarp();
     }
@@ -302,7 +314,8 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_decode_kernel(AttnParams p)
     }
     float* myP = Ps + warp * GMAX * 32;
     const size_t row_stride = (size_t)p.Hkv * hd;        // of a key row
-    const size_t vrow_stride = (size_t)p.Hkv * hdv;      // of a value row
+    const size_t vrow_stride = p.v_shared ? (size_t)hdv : (size_t)p.Hkv * hdv;      // of a value row
+    const size_t vhead = p.v_shared ? 0 : (size_t)kvh * hdv;                       // this kv head's place in it
 
     for (int kb = klo + warp * BK; kb < khi; kb += NWARPS * BK) {
         const int kpos = kb + lane;
@@ -319,7 +332,7 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_decode_kernel(AttnParams p)
             for (int j = 0; j < BK; ++j) {
                 const size_t sj = __shfl_sync(0xffffffffu, slot, j);
                 v0r[j] = v1r[j] = 0.0f;
-                if (j < nkeys && d < hdv) Vec16<T>::load2(vc + sj * vrow_stride + (size_t)kvh * hdv + d, v0r[j], v1r[j]);
+                if (j < nkeys && d < hdv) Vec16<T>::load2(vc + sj * vrow_stride + vhead + d, v0r[j], v1r[j]);
             }
         }
         float dot[GMAX];
@@ -375,7 +388,7 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_decode_kernel(AttnParams p)
 #pragma unroll 8
             for (int j = 0; j < nkeys; ++j) {
                 const size_t sj = __shfl_sync(0xffffffffu, slot, j);
-                const T* vr = vc + sj * vrow_stride + (size_t)kvh * hdv;
+                const T* vr = vc + sj * vrow_stride + vhead;
 #pragma unroll
                 for (int n = 0; n < NPMAX; ++n) {
                     const int d = n * 64 + 2 * lane;
@@ -434,7 +447,7 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_decode_kernel(AttnParams p)
         }
         if (p.nsplit == 1) {
             if (p.sinks) L += expf(p.sinks[kvh * G + g] - M);
-            ((T*)p.out)[((size_t)row0 * p.Hq + kvh * G + g) * hdv + d] = llb_from_float<T>(a / L);
+            store_out<T>(p, ((size_t)row0 * p.Hq + kvh * G + g) * hdv + d, a / L);
         } else {
             p.part_acc[(base + g) * hdv + d] = a;
             if (d == 0) {
@@ -537,12 +550,15 @@ LLB_EXPORT long long llb_attention_scratch_floats(int num_tiles, int Hq, int hd,
 // window: > 0 the latest keys, < 0 the query's own block of -window positions, 0 every earlier key (llb_first_visible).  sinks [Hq] float or null: exp(sinks[h]) is added once to head h's
 // softmax denominator (a logit without key or value, not scaled).  scratch: num_tiles*Hq*BQ*nsplit*(hdv+2) floats
 // when nsplit > 1, else unused.
-LLB_EXPORT int llb_paged_attention_ex(const void* q, const void* k_cache, const void* v_cache, void* out, int dtype,
-                                      const int* tile_span, const int* tile_q0, int num_tiles, const int* span_row,
-                                      const int* span_len, const int* span_pos, const int* block_table,
-                                      int max_pages, int page_size, int Hq, int Hkv, int hd, int hdv,
-                                      const float* sinks, int window, float scale, int BQ, int nsplit, float* scratch,
-                                      cudaStream_t stream) {
+// v_shared != 0: v_cache is [slots, hdv] and every query head reads the whole row (out [T, Hq, hdv]): the products of a
+// head's softmax weights with the values of ALL kv heads, for mixers that combine heads' weights after the softmax.
+// out_f32 != 0: out is float whatever `dtype` says.
+LLB_EXPORT int llb_paged_attention_shared(const void* q, const void* k_cache, const void* v_cache, void* out, int dtype,
+                                          const int* tile_span, const int* tile_q0, int num_tiles, const int* span_row,
+                                          const int* span_len, const int* span_pos, const int* block_table,
+                                          int max_pages, int page_size, int Hq, int Hkv, int hd, int hdv,
+                                          const float* sinks, int window, float scale, int BQ, int nsplit, float* scratch,
+                                          int v_shared, int out_f32, cudaStream_t stream) {
     if (num_tiles == 0) return 0;
     LLB_REQUIRE(num_tiles > 0 && Hq > 0 && Hkv > 0 && hd > 0 && hdv > 0 && page_size > 0 && max_pages > 0 && BQ > 0,
                 "attention: bad sizes");
@@ -557,11 +573,23 @@ LLB_EXPORT int llb_paged_attention_ex(const void* q, const void* k_cache, const 
     p.max_pages = max_pages; p.page_size = page_size; p.Hq = Hq; p.Hkv = Hkv; p.hd = hd;
     p.window = window; p.BQ = BQ; p.nsplit = nsplit; p.scale = scale;
     p.hdv = hdv; p.sinks = sinks;
+    p.v_shared = v_shared ? 1 : 0; p.out_f32 = out_f32 ? 1 : 0;
     p.part_acc = scratch;
     p.part_ml = scratch ? scratch + (size_t)num_tiles * Hq * BQ * nsplit * hdv : nullptr;
     if (dtype == LLB_F32) return launch_attention<float>(p, num_tiles, stream);
     if (dtype == LLB_BF16) return launch_attention<__nv_bfloat16>(p, num_tiles, stream);
     return llb_fail("attention: unknown dtype %d", dtype);
+}
+
+LLB_EXPORT int llb_paged_attention_ex(const void* q, const void* k_cache, const void* v_cache, void* out, int dtype,
+                                      const int* tile_span, const int* tile_q0, int num_tiles, const int* span_row,
+                                      const int* span_len, const int* span_pos, const int* block_table,
+                                      int max_pages, int page_size, int Hq, int Hkv, int hd, int hdv,
+                                      const float* sinks, int window, float scale, int BQ, int nsplit, float* scratch,
+                                      cudaStream_t stream) {
+    return llb_paged_attention_shared(q, k_cache, v_cache, out, dtype, tile_span, tile_q0, num_tiles, span_row, span_len,
+                                      span_pos, block_table, max_pages, page_size, Hq, Hkv, hd, hdv, sinks, window, scale,
+                                      BQ, nsplit, scratch, 0, 0, stream);
 }
 
 // Ordinary attention: values as wide as keys, no sinks.

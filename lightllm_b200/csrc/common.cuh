@@ -56,9 +56,14 @@ __device__ __forceinline__ float llb_silu(float x) { return x / (1.0f + expf(-x)
 // The gated activations of a feed-forward, on a (gate, up) pair in float.
 //   kind 0  SiLU gate:            silu(g) * u
 //   kind 1  clamped swish gate:   g' = min(g, limit), u' = clamp(u, -limit, limit);  g' * sigmoid(alpha * g') * (u' + up_shift)
-enum LlbGlu { LLB_GLU_SILU = 0, LLB_GLU_CLAMPED_SWISH = 1 };
+//   kind 2  GELU gate, tanh form: 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))) * u
+enum LlbGlu { LLB_GLU_SILU = 0, LLB_GLU_CLAMPED_SWISH = 1, LLB_GLU_GELU_TANH = 2 };
+__device__ __forceinline__ float llb_gelu_tanh(float g) {
+    return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+}
 __device__ __forceinline__ float llb_glu(float g, float u, int kind, float alpha, float limit, float up_shift) {
     if (kind == LLB_GLU_SILU) return llb_silu(g) * u;
+    if (kind == LLB_GLU_GELU_TANH) return llb_gelu_tanh(g) * u;
     g = fminf(g, limit);
     u = fminf(fmaxf(u, -limit), limit);
     return g / (1.0f + expf(-alpha * g)) * (u + up_shift);

@@ -67,3 +67,89 @@ LLB_EXPORT int llb_cast_add(const void* src, int src_dtype, void* dst, int dst_d
         return launch_cast<__nv_bfloat16, __nv_bfloat16>(src, dst, n, accumulate, stream);
     return llb_fail("cast_add: unknown dtypes %d, %d", src_dtype, dst_dtype);
 }
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Float helpers of layers whose branches are scaled or normed before they join the stream.
+namespace {
+
+// dst[t, :] += scale * x[t, :] / sqrt(mean(x[t, :]^2) + eps) * w        one warp a row, all float but w
+template <typename TW>
+__global__ void __launch_bounds__(256) rmsnorm_add_kernel(const float* __restrict__ x, const TW* __restrict__ w,
+                                                          float* __restrict__ dst, long long T, int D, float eps, float scale) {
+    const int lane = threadIdx.x & 31;
+    const long long t = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (t >= T) return;
+    const float* xr = x + t * D;
+    float ss = 0.0f;
+    for (int d = lane; d < D; d += 32) ss = fmaf(xr[d], xr[d], ss);
+    const float inv = scale / sqrtf(llb_warp_sum(ss) / (float)D + eps);
+    float* o = dst + t * D;
+    for (int d = lane; d < D; d += 32) o[d] += xr[d] * inv * llb_to_float(w[d]);
+}
+
+// y[i] += a * x[i]; optionally the new y once more in bf16
+__global__ void axpy_kernel(const float* __restrict__ x, float* __restrict__ y, __nv_bfloat16* __restrict__ copy, long long n, float a) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const float v = fmaf(a, x[i], y[i]);
+        y[i] = v;
+        if (copy) copy[i] = __float2bfloat16_rn(v);
+    }
+}
+
+// x[t, d] += v[d]
+template <typename TV>
+__global__ void add_row_kernel(float* __restrict__ x, const TV* __restrict__ v, long long n, int D) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) x[i] += llb_to_float(v[i % D]);
+}
+
+// x[i] = cap * tanh(x[i] / cap)
+__global__ void softcap_kernel(float* __restrict__ x, long long n, float cap) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) x[i] = cap * tanhf(x[i] / cap);
+}
+
+inline int grid_for(long long n) { return (int)((n + 255) / 256 < 1184 ? (n + 255) / 256 : 1184); }
+
+}  // namespace
+
+// dst [T, D] float += scale * rmsnorm(x [T, D] float) * w [D] (float or bf16): a normed branch joining a float sum.
+LLB_EXPORT int llb_rmsnorm_add(const float* x, const void* w, int w_dtype, float* dst, long long T, int D, float eps,
+                               float scale, cudaStream_t stream) {
+    if (T == 0) return 0;
+    LLB_REQUIRE(T > 0 && D > 0 && x && w && dst, "rmsnorm_add: bad arguments");
+    const unsigned blocks = (unsigned)((T + 7) / 8);
+    if (w_dtype == LLB_F32) rmsnorm_add_kernel<float><<<blocks, 256, 0, stream>>>(x, (const float*)w, dst, T, D, eps, scale);
+    else if (w_dtype == LLB_BF16)
+        rmsnorm_add_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(x, (const __nv_bfloat16*)w, dst, T, D, eps, scale);
+    else return llb_fail("rmsnorm_add: unknown weight dtype %d", w_dtype);
+    return llb_check_launch("rmsnorm_add");
+}
+
+// y [n] float += a * x [n] float; copy (bf16 [n] or null) receives the new y as well.
+LLB_EXPORT int llb_axpy(const float* x, float* y, void* copy, long long n, float a, cudaStream_t stream) {
+    if (n == 0) return 0;
+    LLB_REQUIRE(n > 0 && x && y, "axpy: bad arguments");
+    axpy_kernel<<<grid_for(n), 256, 0, stream>>>(x, y, (__nv_bfloat16*)copy, n, a);
+    return llb_check_launch("axpy");
+}
+
+// x [T, D] float: every row += v [D] (float or bf16).
+LLB_EXPORT int llb_add_row(float* x, const void* v, int v_dtype, long long T, int D, cudaStream_t stream) {
+    if (T == 0) return 0;
+    LLB_REQUIRE(T > 0 && D > 0 && x && v, "add_row: bad arguments");
+    const long long n = T * D;
+    if (v_dtype == LLB_F32) add_row_kernel<float><<<grid_for(n), 256, 0, stream>>>(x, (const float*)v, n, D);
+    else if (v_dtype == LLB_BF16) add_row_kernel<__nv_bfloat16><<<grid_for(n), 256, 0, stream>>>(x, (const __nv_bfloat16*)v, n, D);
+    else return llb_fail("add_row: unknown dtype %d", v_dtype);
+    return llb_check_launch("add_row");
+}
+
+// x [n] float = cap * tanh(x / cap), in place (soft-capped logits).
+LLB_EXPORT int llb_softcap(float* x, long long n, float cap, cudaStream_t stream) {
+    if (n == 0) return 0;
+    LLB_REQUIRE(n > 0 && x && cap > 0.0f, "softcap: bad arguments");
+    softcap_kernel<<<grid_for(n), 256, 0, stream>>>(x, n, cap);
+    return llb_check_launch("softcap");
+}

@@ -19,7 +19,8 @@ template <typename TX, typename TG, typename TO>
 __global__ void __launch_bounds__(256) head_gate_kernel(const TX* __restrict__ x, const TG* __restrict__ gate,
                                                         long long gate_stride, TO* __restrict__ out, int T, int H, int hd,
                                                         int unit_rms, float eps, int per_head, int act,
-                                                        const float* __restrict__ norm_w) {
+                                                        const float* __restrict__ norm_w, int norm_w_heads,
+                                                        const float* __restrict__ den) {
     const int lane = threadIdx.x & 31;
     const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (item >= (long long)T * H) return;
@@ -27,14 +28,17 @@ __global__ void __launch_bounds__(256) head_gate_kernel(const TX* __restrict__ x
     const TX* xr = x + ((size_t)t * H + h) * hd;
     TO* o = out + ((size_t)t * H + h) * hd;
     float inv = 1.0f;
+    const float pre = den ? 1.0f / den[(size_t)t * H + h] : 1.0f;          // a head's denominator, applied before the norm
     if (unit_rms) {
         float ss = 0.0f;
         for (int d = lane; d < hd; d += 32) {
-            const float v = llb_to_float(xr[d]);
+            const float v = llb_to_float(xr[d]) * pre;
             ss += v * v;
         }
         inv = 1.0f / sqrtf(llb_warp_sum(ss) / (float)hd + eps);
     }
+    inv *= pre;
+    if (norm_w && norm_w_heads) norm_w += (size_t)h * hd;
     const TG* gr = gate + (size_t)t * gate_stride + (per_head ? h : (size_t)h * hd);
     for (int d = lane; d < hd; d += 32) {
         const float z = llb_to_float(gr[per_head ? 0 : d]);
@@ -47,10 +51,12 @@ __global__ void __launch_bounds__(256) head_gate_kernel(const TX* __restrict__ x
 
 template <typename TX, typename TG, typename TO>
 int launch_head_gate(const void* x, const void* gate, long long gate_stride, void* out, int T, int H, int hd,
-                     int unit_rms, float eps, int per_head, int act, const float* norm_w, cudaStream_t s) {
+                     int unit_rms, float eps, int per_head, int act, const float* norm_w, int norm_w_heads,
+                     const float* den, cudaStream_t s) {
     const long long items = (long long)T * H;
     head_gate_kernel<TX, TG, TO><<<(unsigned)((items + 7) / 8), 256, 0, s>>>(
-        (const TX*)x, (const TG*)gate, gate_stride, (TO*)out, T, H, hd, unit_rms, eps, per_head, act, norm_w);
+        (const TX*)x, (const TG*)gate, gate_stride, (TO*)out, T, H, hd, unit_rms, eps, per_head, act, norm_w,
+        norm_w_heads, den);
     return llb_check_launch("head_gate");
 }
 
@@ -77,17 +83,79 @@ LLB_EXPORT int llb_glu_act(const void* in, void* out, int dtype, int M, int I, i
 // (per_head) or H*hd; out [T, H, hd] in the activation dtype.  out = (unit_rms ? x / sqrt(mean_head(x^2) + eps) : x)
 // * act(gate), act 0 = sigmoid, 1 = SiLU.  x_dtype: dtype of x; dtype: of gate and out.  norm_w: float [hd] or null, a weight
 // on the (normed) head shared by all heads, applied before the gate.
-LLB_EXPORT int llb_head_gate(const void* x, int x_dtype, const void* gate, long long gate_stride, void* out, int dtype,
-                             int T, int H, int hd, int unit_rms, float eps, int per_head, int act, const float* norm_w,
-                             cudaStream_t stream) {
+// llb_head_gate_ex: norm_w_heads != 0: norm_w is [H, hd], a weight of its own for every head; den: float [T, H] or null,
+// every head's x is first divided by den[t, h] (before the norm).
+LLB_EXPORT int llb_head_gate_ex(const void* x, int x_dtype, const void* gate, long long gate_stride, void* out, int dtype,
+                                int T, int H, int hd, int unit_rms, float eps, int per_head, int act, const float* norm_w,
+                                int norm_w_heads, const float* den, cudaStream_t stream) {
     if (T == 0) return 0;
     LLB_REQUIRE(T > 0 && H > 0 && hd > 0 && x && gate && out, "head_gate: bad arguments");
     LLB_REQUIRE(act == 0 || act == 1, "head_gate: unknown activation %d", act);
     if (x_dtype == LLB_F32 && dtype == LLB_F32)
-        return launch_head_gate<float, float, float>(x, gate, gate_stride, out, T, H, hd, unit_rms, eps, per_head, act, norm_w, stream);
+        return launch_head_gate<float, float, float>(x, gate, gate_stride, out, T, H, hd, unit_rms, eps, per_head, act, norm_w, norm_w_heads, den, stream);
     if (x_dtype == LLB_F32 && dtype == LLB_BF16)
-        return launch_head_gate<float, __nv_bfloat16, __nv_bfloat16>(x, gate, gate_stride, out, T, H, hd, unit_rms, eps, per_head, act, norm_w, stream);
+        return launch_head_gate<float, __nv_bfloat16, __nv_bfloat16>(x, gate, gate_stride, out, T, H, hd, unit_rms, eps, per_head, act, norm_w, norm_w_heads, den, stream);
     if (x_dtype == LLB_BF16 && dtype == LLB_BF16)
-        return launch_head_gate<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(x, gate, gate_stride, out, T, H, hd, unit_rms, eps, per_head, act, norm_w, stream);
+        return launch_head_gate<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(x, gate, gate_stride, out, T, H, hd, unit_rms, eps, per_head, act, norm_w, norm_w_heads, den, stream);
     return llb_fail("head_gate: unsupported dtypes %d, %d", x_dtype, dtype);
+}
+
+LLB_EXPORT int llb_head_gate(const void* x, int x_dtype, const void* gate, long long gate_stride, void* out, int dtype,
+                             int T, int H, int hd, int unit_rms, float eps, int per_head, int act, const float* norm_w,
+                             cudaStream_t stream) {
+    return llb_head_gate_ex(x, x_dtype, gate, gate_stride, out, dtype, T, H, hd, unit_rms, eps, per_head, act, norm_w, 0,
+                            nullptr, stream);
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Heads mixed after the softmax.  An attention whose heads' weights are combined, w'_h = sum_g talk[h, g] w_g, before
+// head h applies them to the values of its own kv head, equals a combination of plain attention outputs: with
+// o[t, g, c, :] = sum_j w_g(t, j) v_c(j) (query head g over the values of kv head c, from the attention kernel with
+// shared value rows),    out[t, h, :] = sum_g talk[h, g] * o[t, g, kv(h), :]    times act(gate[t, h, :]).
+// One warp per (token, head); sums in float.
+namespace {
+template <typename TO_, typename TG>
+__global__ void __launch_bounds__(256) talk_mix_kernel(const TO_* __restrict__ o, const float* __restrict__ talk,
+                                                       const TG* __restrict__ gate, long long gate_stride,
+                                                       TG* __restrict__ out, int T, int H, int G, int vd, int gated) {
+    const int lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= (long long)T * H) return;
+    const int t = (int)(item / H), h = (int)(item - (long long)t * H);
+    const int c = h / (H / G);
+    const TO_* row = o + (size_t)t * H * G * vd + (size_t)c * vd;          // + g * G * vd: query head g
+    const float* w = talk ? talk + (size_t)h * H : nullptr;
+    const TG* gr = gate + (size_t)t * gate_stride + (size_t)h * vd;
+    for (int d = lane; d < vd; d += 32) {
+        float a = 0.0f;
+        if (w) {
+            for (int g = 0; g < H; ++g) a = fmaf(w[g], llb_to_float(row[(size_t)g * G * vd + d]), a);
+        } else {
+            a = llb_to_float(row[(size_t)h * G * vd + d]);
+        }
+        if (gated) a *= 1.0f / (1.0f + expf(-llb_to_float(gr[d])));
+        out[((size_t)t * H + h) * vd + d] = llb_from_float<TG>(a);
+    }
+}
+}  // namespace
+
+// o [T, H, G, vd] (float, or the activation dtype); talk float [H, H] or null (no mixing: out_h = o[h, kv(h)]);
+// gate: row t at gate + t * gate_stride holds H * vd values, the output is multiplied by their sigmoid (null: no gate);
+// out [T, H, vd] in the activation dtype `dtype`.
+LLB_EXPORT int llb_talk_mix(const void* o, int o_dtype, const float* talk, const void* gate, long long gate_stride,
+                            void* out, int dtype, int T, int H, int G, int vd, cudaStream_t stream) {
+    if (T == 0) return 0;
+    LLB_REQUIRE(T > 0 && H > 0 && G > 0 && H % G == 0 && vd > 0 && o && out, "talk_mix: bad arguments");
+    const long long items = (long long)T * H;
+    const unsigned blocks = (unsigned)((items + 7) / 8);
+    const int gated = gate != nullptr;
+    if (!gated) gate = out;
+    if (o_dtype == LLB_F32 && dtype == LLB_F32)
+        talk_mix_kernel<float, float><<<blocks, 256, 0, stream>>>((const float*)o, talk, (const float*)gate, gate_stride, (float*)out, T, H, G, vd, gated);
+    else if (o_dtype == LLB_F32 && dtype == LLB_BF16)
+        talk_mix_kernel<float, __nv_bfloat16><<<blocks, 256, 0, stream>>>((const float*)o, talk, (const __nv_bfloat16*)gate, gate_stride, (__nv_bfloat16*)out, T, H, G, vd, gated);
+    else if (o_dtype == LLB_BF16 && dtype == LLB_BF16)
+        talk_mix_kernel<__nv_bfloat16, __nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)o, talk, (const __nv_bfloat16*)gate, gate_stride, (__nv_bfloat16*)out, T, H, G, vd, gated);
+    else return llb_fail("talk_mix: unsupported dtypes %d, %d", o_dtype, dtype);
+    return llb_check_launch("talk_mix");
 }

@@ -245,13 +245,17 @@ def paged_attention_simt(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
                          block_table: torch.Tensor, max_pages: int, page_size: int,
                          num_heads: int, num_kv_heads: int, head_dim: int, window: int, scale: float,
                          bq: int, nsplit: int = 1, scratch: Optional[torch.Tensor] = None,
-                         v_head_dim: Optional[int] = None, sinks: Optional[torch.Tensor] = None) -> None:
+                         v_head_dim: Optional[int] = None, sinks: Optional[torch.Tensor] = None,
+                         v_shared: bool = False) -> None:
     """Attention of every query row of the listed tiles over its request's pages.  ``v_head_dim``: width of a value
     row (and of an output row) when it differs from the keys'; ``v_cache`` may be ``k_cache`` itself (values read out
-    of the key rows).  ``sinks`` float32 [num_heads]: ``exp(sinks[h])`` joins head h's softmax denominator once."""
+    of the key rows).  ``sinks`` float32 [num_heads]: ``exp(sinks[h])`` joins head h's softmax denominator once.
+    ``v_shared``: a slot's value row (``v_head_dim`` wide: all kv heads side by side) is read whole by every query head,
+    so ``out`` [T, num_heads, v_head_dim] holds each head's weights applied to the values of every kv head.  ``out`` may
+    be float32 under bfloat16 inputs."""
     hdv = head_dim if v_head_dim is None else v_head_dim
-    if k_cache.dtype != q.dtype or v_cache.dtype != q.dtype or out.dtype != q.dtype:
-        raise KernelError("attention: q, caches and out must share a dtype")
+    if k_cache.dtype != q.dtype or v_cache.dtype != q.dtype or out.dtype not in (q.dtype, torch.float32):
+        raise KernelError("attention: q and the caches must share a dtype, out has it or is float32")
     if sinks is not None and (sinks.dtype != torch.float32 or sinks.numel() != num_heads):
         raise KernelError(f"attention: sinks must be float32 [{num_heads}]")
     if out.numel() != q.shape[0] * num_heads * hdv:
@@ -260,12 +264,13 @@ def paged_attention_simt(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
         need = attention_scratch_floats(num_tiles, num_heads, hdv, bq, nsplit)
         if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need:
             raise KernelError(f"attention: nsplit={nsplit} needs {need} floats of scratch")
-    _check(lib().llb_paged_attention_ex(
+    _check(lib().llb_paged_attention_shared(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _dt(q),
         _i32(tile_span, "tile_span"), _i32(tile_q0, "tile_q0"), num_tiles,
         _i32(span_row, "span_row"), _i32(span_len, "span_len"), _i32(span_pos, "span_pos"),
         _i32(block_table, "block_table"), max_pages, page_size, num_heads, num_kv_heads, head_dim, hdv, _ptr(sinks),
-        window, ctypes.c_float(scale), bq, nsplit, _ptr(scratch), _stream()))
+        window, ctypes.c_float(scale), bq, nsplit, _ptr(scratch), 1 if v_shared else 0,
+        1 if out.dtype == torch.float32 and q.dtype != torch.float32 else 0, _stream()))
 
 
 def _f32(t: Optional[torch.Tensor], what: str) -> Optional[int]:
@@ -290,7 +295,7 @@ def layernorm(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor
                                R, D, ctypes.c_float(eps), 1 if accumulate else 0, _ptr(copy), _stream()))
 
 
-GLU_SILU, GLU_CLAMPED_SWISH = 0, 1
+GLU_SILU, GLU_CLAMPED_SWISH, GLU_GELU_TANH = 0, 1, 2
 
 
 def glu_act(x: torch.Tensor, out: torch.Tensor, kind: int, alpha: float = 1.0, limit: float = 0.0,
@@ -306,9 +311,10 @@ def glu_act(x: torch.Tensor, out: torch.Tensor, kind: int, alpha: float = 1.0, l
 
 def head_gate(x: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, num_heads: int, head_dim: int,
               per_head: bool, act: str, unit_rms: bool = False, eps: float = 0.0,
-              norm_weight: Optional[torch.Tensor] = None) -> None:
+              norm_weight: Optional[torch.Tensor] = None, denominator: Optional[torch.Tensor] = None) -> None:
     """out[t,h,:] = (x[t,h,:], or x / rms(x) over the head with ``unit_rms``) * act(gate), act ``sigmoid`` or ``silu``;
-    ``norm_weight`` (float32 [head_dim], shared by the heads) multiplies the normed head before the gate.
+    ``norm_weight`` (float32, [head_dim] shared by the heads or [num_heads * head_dim]) multiplies the normed head before
+    the gate; ``denominator`` (float32 [T, H]) divides every head's x first, before the norm.
     ``gate`` is a [T, H] (``per_head``) or [T, H*head_dim] view whose rows may be strided (columns of a wider tensor).
     x float32 or the dtype of gate and out."""
     T = x.shape[0]
@@ -317,14 +323,127 @@ def head_gate(x: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, num_heads:
         raise KernelError(f"head_gate: gate must be {out.dtype} [{T},{width}] with unit inner stride")
     if x.numel() != T * num_heads * head_dim or out.numel() != x.numel():
         raise KernelError("head_gate: sizes do not fit")
-    if norm_weight is not None and norm_weight.numel() != head_dim:
-        raise KernelError("head_gate: norm_weight must have one weight per dimension of a head")
+    if norm_weight is not None and norm_weight.numel() not in (head_dim, num_heads * head_dim):
+        raise KernelError("head_gate: norm_weight must have one weight per dimension of a head, or of every head")
+    if denominator is not None and (denominator.dtype != torch.float32 or denominator.numel() != T * num_heads):
+        raise KernelError(f"head_gate: the denominator must be float32 [{T},{num_heads}]")
     if not gate.is_cuda:
         raise KernelError("tensor is not on a CUDA device; there is no CPU path")
-    _check(lib().llb_head_gate(_ptr(x), _dt(x), ctypes.c_void_p(gate.data_ptr()), ctypes.c_longlong(gate.stride(0)),
-                               _ptr(out), _dt(out), T, num_heads, head_dim, 1 if unit_rms else 0, ctypes.c_float(eps),
-                               1 if per_head else 0, {"sigmoid": 0, "silu": 1}[act], _f32(norm_weight, "norm_weight"),
-                               _stream()))
+    per_head_weight = norm_weight is not None and norm_weight.numel() != head_dim
+    _check(lib().llb_head_gate_ex(_ptr(x), _dt(x), ctypes.c_void_p(gate.data_ptr()), ctypes.c_longlong(gate.stride(0)),
+                                  _ptr(out), _dt(out), T, num_heads, head_dim, 1 if unit_rms else 0, ctypes.c_float(eps),
+                                  1 if per_head else 0, {"sigmoid": 0, "silu": 1}[act], _f32(norm_weight, "norm_weight"),
+                                  1 if per_head_weight else 0, _f32(denominator, "denominator"), _stream()))
+
+
+def talk_mix(o: torch.Tensor, talk: Optional[torch.Tensor], gate: Optional[torch.Tensor], out: torch.Tensor,
+             num_heads: int, num_kv_heads: int, v_head_dim: int) -> None:
+    """out[t, h, :] = sum_g talk[h, g] * o[t, g, kv(h), :], times sigmoid(gate[t, h, :]): ``o`` [T, H, G, vdim] holds every
+    query head's softmax weights applied to the values of every kv head (float32 or the activation dtype), ``talk``
+    float32 [H, H] mixes the heads (``None``: head h takes ``o[t, h, kv(h)]``), ``gate`` [T, H*vdim] may be columns of a
+    wider tensor (``None``: no gate); ``out`` [T, H*vdim] in the activation dtype."""
+    T = out.shape[0]
+    H, G, vd = num_heads, num_kv_heads, v_head_dim
+    if o.numel() != T * H * G * vd or out.numel() != T * H * vd or not o.is_contiguous() or not out.is_contiguous():
+        raise KernelError("talk_mix: sizes do not fit")
+    if talk is not None and (talk.dtype != torch.float32 or tuple(talk.shape) != (H, H) or not talk.is_contiguous()):
+        raise KernelError(f"talk_mix: the mixing matrix must be float32 [{H},{H}]")
+    if gate is not None and (gate.dim() != 2 or tuple(gate.shape) != (T, H * vd) or gate.stride(1) != 1 or gate.dtype != out.dtype):
+        raise KernelError(f"talk_mix: gate must be {out.dtype} [{T},{H * vd}] with unit inner stride")
+    _check(lib().llb_talk_mix(_ptr(o), _dt(o), _ptr(talk), None if gate is None else ctypes.c_void_p(gate.data_ptr()),
+                              ctypes.c_longlong(0 if gate is None else gate.stride(0)), _ptr(out), _dt(out), T, H, G, vd,
+                              _stream()))
+
+
+def rmsnorm_add(x: torch.Tensor, weight: torch.Tensor, eps: float, dst: torch.Tensor, scale: float = 1.0) -> None:
+    """dst += scale * rmsnorm(x) * weight, x and dst float32 [T, D]: a normed branch joining a float sum."""
+    T, D = x.shape
+    if x.dtype != torch.float32 or dst.dtype != torch.float32 or tuple(dst.shape) != (T, D) or weight.numel() != D:
+        raise KernelError("rmsnorm_add: x and dst must be float32 of one shape, weight one value a column")
+    _check(lib().llb_rmsnorm_add(_ptr(x), _ptr(weight), _dt(weight), _ptr(dst), ctypes.c_longlong(T), D,
+                                 ctypes.c_float(eps), ctypes.c_float(scale), _stream()))
+
+
+def axpy(x: torch.Tensor, y: torch.Tensor, a: float, copy: Optional[torch.Tensor] = None) -> None:
+    """y += a * x (float32, equal sizes); ``copy`` (bfloat16) receives the new y as well."""
+    if x.dtype != torch.float32 or y.dtype != torch.float32 or x.numel() != y.numel():
+        raise KernelError("axpy: x and y must be float32 of equal size")
+    if copy is not None and (copy.dtype != torch.bfloat16 or copy.numel() != y.numel()):
+        raise KernelError("axpy: the copy must be bfloat16 of y's size")
+    _check(lib().llb_axpy(_ptr(x), _ptr(y), _ptr(copy), ctypes.c_longlong(y.numel()), ctypes.c_float(a), _stream()))
+
+
+def add_row(x: torch.Tensor, v: torch.Tensor) -> None:
+    """x[t, :] += v for every row of the float32 [T, D] tensor x."""
+    T, D = x.shape
+    if x.dtype != torch.float32 or v.numel() != D or not v.is_contiguous():
+        raise KernelError("add_row: x must be float32 [T, D] and v hold D values")
+    _check(lib().llb_add_row(_ptr(x), _ptr(v), _dt(v), ctypes.c_longlong(T), D, _stream()))
+
+
+def softcap(x: torch.Tensor, cap: float) -> None:
+    """x = cap * tanh(x / cap) in place (float32)."""
+    if x.dtype != torch.float32 or not cap > 0:
+        raise KernelError("softcap: x must be float32 and the cap positive")
+    _check(lib().llb_softcap(_ptr(x), ctypes.c_longlong(x.numel()), ctypes.c_float(cap), _stream()))
+
+
+def memory_gates(pre: torch.Tensor, i_off: int, f_off: int, bias_i: Optional[torch.Tensor], bias_f: Optional[torch.Tensor],
+                 cap: float, ctx_spans, num_heads: int, state: torch.Tensor, m_off: int, keep: torch.Tensor,
+                 take: torch.Tensor, floor: torch.Tensor) -> None:
+    """The gates of a matrix memory (csrc/matrix_memory.cu) for every token and head of the step: ``pre`` float32 [T, C]
+    holds the pre-activations of the input gates in columns ``i_off ..`` and of the forget gates in ``f_off ..`` (one a
+    head; ``bias_*`` float32 [H] are added); ``keep``, ``take``, ``floor`` float32 [T, H] receive ``exp(f + m' - m)``,
+    ``exp(i - m)``, ``exp(-m)``; a request's running maximum m [H] lives at ``m_off`` floats into its slot of ``state``."""
+    T, C = pre.shape
+    H = num_heads
+    span_row, span_len, span_pos, span_slot, num_spans = ctx_spans
+    base, stride = _state_base(state)
+    if pre.dtype != torch.float32 or not pre.is_contiguous() or max(i_off, f_off) + H > C:
+        raise KernelError("memory_gates: pre must be contiguous float32 and hold both gates' columns")
+    if m_off + H > stride or any(t.dtype != torch.float32 or t.numel() != T * H for t in (keep, take, floor)):
+        raise KernelError("memory_gates: outputs must be float32 [T, H] and m must fit in a state slot")
+    _check(lib().llb_memory_gates(_ptr(pre), ctypes.c_longlong(C), i_off, f_off, _f32(bias_i, "bias_i"),
+                                  _f32(bias_f, "bias_f"), ctypes.c_float(cap), _i32(span_row, "span_row"),
+                                  _i32(span_len, "span_len"), _i32(span_pos, "span_pos"), _i32(span_slot, "span_slot"),
+                                  num_spans, H, base, ctypes.c_longlong(stride), ctypes.c_longlong(m_off), _ptr(keep),
+                                  _ptr(take), _ptr(floor), _stream()))
+
+
+def matrix_memory(src: torch.Tensor, q_off: int, k_off: int, v_off: int, q_scale: float, keep: torch.Tensor,
+                  take: torch.Tensor, floor: torch.Tensor, ctx_spans, num_heads: int, head_dim: int, v_head_dim: int,
+                  state: torch.Tensor, s_off: int, out: torch.Tensor, den: torch.Tensor, pieces=None) -> None:
+    """The matrix memory's recurrence over every span of the step (csrc/matrix_memory.cu): q, k [H, dim] and v [H, vdim]
+    are column ranges of ``src`` [T, C]; the gates from :func:`memory_gates`; a request's ``[H, dim, vdim + 1]`` floats (S
+    with n as its last column) live at ``s_off`` into its slot of ``state``; ``out`` float32 [T, H*vdim] receives the
+    numerators ``S^T q`` and ``den`` float32 [T, H] the denominators.  ``pieces`` as :func:`retention` takes them."""
+    T, C = src.shape
+    H, hd, vd = num_heads, head_dim, v_head_dim
+    span_row, span_len, span_pos, span_slot, num_spans = ctx_spans
+    base, stride = _state_base(state)
+    if max(q_off, k_off) + H * hd > C or v_off + H * vd > C or not src.is_contiguous():
+        raise KernelError("matrix_memory: q, k or v lie outside the columns of src")
+    if s_off + H * hd * (vd + 1) > stride:
+        raise KernelError("matrix_memory: the state does not fit in a slot")
+    if out.dtype != torch.float32 or out.numel() != T * H * vd or den.dtype != torch.float32 or den.numel() != T * H:
+        raise KernelError("matrix_memory: out must be float32 [T, H*vdim] and den float32 [T, H]")
+    scratch = piece_keep = None
+    if pieces is None:
+        iota = torch.arange(num_spans, dtype=torch.int32, device=src.device)
+        item_span, item_c, span_first, num_items, chunk = iota, torch.zeros_like(iota), iota, num_spans, 1 << 30
+    else:
+        item_span, item_c, span_first, num_items, chunk = pieces
+    multi = num_items > num_spans
+    if multi:
+        scratch = torch.empty((num_items, H, hd, vd + 1), dtype=torch.float32, device=src.device)
+        piece_keep = torch.empty((num_items, H), dtype=torch.float32, device=src.device)
+    _check(lib().llb_matrix_memory(_ptr(src), _dt(src), ctypes.c_longlong(C), q_off, k_off, v_off, ctypes.c_float(q_scale),
+                                   _ptr(keep), _ptr(take), _ptr(floor), _i32(span_row, "span_row"),
+                                   _i32(span_len, "span_len"), _i32(span_pos, "span_pos"), _i32(span_slot, "span_slot"),
+                                   num_spans, _i32(item_span, "item_span"), _i32(item_c, "item_c"),
+                                   _i32(span_first, "span_first"), num_items, chunk, 1 if multi else 0, H, hd, vd, base,
+                                   ctypes.c_longlong(stride), ctypes.c_longlong(s_off), _ptr(scratch), _ptr(piece_keep),
+                                   _ptr(out), _ptr(den), _stream()))
 
 
 def qkv_prepare(src: torch.Tensor, q_off: int, k_off: int, v_off: int, num_heads: int, num_kv_heads: int,
@@ -412,12 +531,14 @@ class ConvSegment:
     """One of the up to three head groups (q, k, v) that :func:`conv_prepare` makes from the convolved channels:
     ``col0`` first channel, ``heads`` x ``head_dim``, ``act`` None or ``"silu"``, ``rotary_dim`` leading dimensions
     rotated, ``norm`` None, ``"rms"`` (unit root mean square) or ``"unit"`` (unit length) with ``eps``, ``scale`` on
-    the result, ``out`` a dense [T, heads*head_dim] tensor or (``to_cache``) the cache rows [slots, heads, head_dim]."""
+    the result, ``out`` a dense [T, heads*head_dim] tensor or (``to_cache``) the cache rows [slots, heads, head_dim].
+    ``temperature = (coef, every)``: the result is also multiplied by ``1 + coef * ln(floor((pos + 1) / every) + 1)``."""
 
     def __init__(self, col0: int, heads: int, head_dim: int, out: torch.Tensor, to_cache: bool = False, act=None,
-                 rotary_dim: int = 0, norm=None, eps: float = 0.0, scale: float = 1.0):
+                 rotary_dim: int = 0, norm=None, eps: float = 0.0, scale: float = 1.0, temperature=None):
         self.col0, self.heads, self.head_dim, self.out, self.to_cache = col0, heads, head_dim, out, to_cache
         self.act, self.rotary_dim, self.norm, self.eps, self.scale = act, rotary_dim, norm, eps, scale
+        self.temp_coef, self.temp_every = (float(temperature[0]), int(temperature[1])) if temperature else (0.0, 0)
 
 
 def _state_base(state: torch.Tensor):
@@ -459,14 +580,15 @@ def conv_prepare(src: torch.Tensor, c0: int, channels: int, weight: torch.Tensor
             raise KernelError("conv_prepare: a segment's output does not fit")
         if sg.to_cache and tuple(sg.out.shape[1:]) != (sg.heads, sg.head_dim):
             raise KernelError("conv_prepare: a segment's cache plane does not fit")
-    _check(lib().llb_conv_prepare(
+    _check(lib().llb_conv_prepare_temp(
         _ptr(src), _dt(src), ctypes.c_longlong(C), c0, channels, taps, T, _f32(weight, "weight"),
         _i32(span_row, "span_row"), _i32(span_len, "span_len"), _i32(span_pos, "span_pos"), _i32(span_slot, "span_slot"),
         num_spans, base, ctypes.c_longlong(stride), ctypes.c_longlong(tail_off), _i32(slot_mapping, "slot_mapping"),
         _f32(freq, "freq"), ctypes.c_float(rot_scale), n, I(*[s.col0 for s in segments]), I(*[s.heads for s in segments]),
         I(*[s.head_dim for s in segments]), I(*[{None: 0, "silu": 1}[s.act] for s in segments]),
         I(*[s.rotary_dim for s in segments]), I(*[CONV_NORMS[s.norm] for s in segments]),
-        Fl(*[s.eps for s in segments]), Fl(*[s.scale for s in segments]), P(*[s.out.data_ptr() for s in segments]),
+        Fl(*[s.eps for s in segments]), Fl(*[s.scale for s in segments]), Fl(*[s.temp_coef for s in segments]),
+        I(*[s.temp_every for s in segments]), P(*[s.out.data_ptr() for s in segments]),
         I(*[_dt(s.out) for s in segments]), I(*[1 if s.to_cache else 0 for s in segments]), 1 if fuse_tail else 0,
         _stream()))
 

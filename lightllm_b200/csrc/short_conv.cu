@@ -6,6 +6,8 @@
 //     rotation  of the first rotary_dim dimensions of a head, pairs (2i, 2i + 1), angle = pos * freq[i], cos and sin
 //               times `rot_scale` (a frequency table and a magnitude factor: plain or YaRN-scaled rotary positions)
 //     head norm none, x / sqrt(mean(x^2) + eps) or x / sqrt(sum(x^2) + eps), then times `post_scale`
+//     and, where a segment has a temperature by position (`temp_every` > 0), times
+//               1 + temp_coef * ln(floor((pos + 1) / temp_every) + 1)
 //
 // The result goes to a dense tensor or to the cache rows of the new tokens.  The inputs of the taps - 1 positions before
 // a span's first token come from the request's state slot (`tail`: [taps - 1, C] floats, the last projected values of
@@ -31,6 +33,8 @@ struct ConvSegment {
     int rotary_dim;      // 0: no rotation
     int norm;            // 0 none, 1 unit root mean square, 2 unit length
     float eps, post_scale;
+    float temp_coef;     // a factor that grows with the position in steps of temp_every positions (0: none)
+    int temp_every;
     void* out;           // dense [T, heads * hd], or cache rows [slots, heads, hd] with `to_cache`
     int out_dtype;       // LLB_F32 / LLB_BF16
     int to_cache;
@@ -116,6 +120,7 @@ __global__ void __launch_bounds__(128) conv_prepare_kernel(ConvParams p) {
         ss += y[i][0] * y[i][0] + y[i][1] * y[i][1];
     }
     float mul = sg.post_scale;
+    if (sg.temp_every > 0) mul *= 1.0f + sg.temp_coef * logf((float)((pos + 1) / sg.temp_every) + 1.0f);
     if (sg.norm != 0) {
         ss = llb_warp_sum(ss);
         mul *= 1.0f / sqrtf((sg.norm == 1 ? ss / (float)hd : ss) + sg.eps);
@@ -195,15 +200,18 @@ __global__ void __launch_bounds__(256) conv_tail_kernel(ConvParams p) {
 // parallel arrays of `num_segments` entries: first channel, heads, head size, activation (0 none, 1 SiLU), rotary_dim (0
 // none; pairs (2i, 2i+1) by freq [rotary_dim / 2] and rot_scale), norm (0 none, 1 unit root mean square, 2 unit length)
 // with eps, post_scale, output pointer with dtype, and whether the output is the cache (rows by slot_mapping [T]).
+// llb_conv_prepare_temp takes two more arrays: a segment's temperature by position (coefficient, and the number of
+// positions a step lasts; 0 for a segment without).
 // fuse_tail != 0 (only when every span is one token): the new tails are written here and llb_conv_tail_update is not needed.
-LLB_EXPORT int llb_conv_prepare(const void* src, int src_dtype, long long row_stride, int c0, int C, int taps, int T,
-                                const float* w, const int* span_row, const int* span_len, const int* span_pos,
-                                const int* span_slot, int num_spans, float* state, long long state_stride,
-                                long long tail_off, const int* slot_mapping, const float* freq, float rot_scale,
-                                int num_segments, const int* seg_col0, const int* seg_heads, const int* seg_hd,
-                                const int* seg_act, const int* seg_rotary, const int* seg_norm, const float* seg_eps,
-                                const float* seg_scale, void* const* seg_out, const int* seg_out_dtype,
-                                const int* seg_to_cache, int fuse_tail, cudaStream_t stream) {
+LLB_EXPORT int llb_conv_prepare_temp(const void* src, int src_dtype, long long row_stride, int c0, int C, int taps, int T,
+                                     const float* w, const int* span_row, const int* span_len, const int* span_pos,
+                                     const int* span_slot, int num_spans, float* state, long long state_stride,
+                                     long long tail_off, const int* slot_mapping, const float* freq, float rot_scale,
+                                     int num_segments, const int* seg_col0, const int* seg_heads, const int* seg_hd,
+                                     const int* seg_act, const int* seg_rotary, const int* seg_norm, const float* seg_eps,
+                                     const float* seg_scale, const float* seg_temp_coef, const int* seg_temp_every,
+                                     void* const* seg_out, const int* seg_out_dtype, const int* seg_to_cache,
+                                     int fuse_tail, cudaStream_t stream) {
     if (T == 0) return 0;
     LLB_REQUIRE(!fuse_tail || T == num_spans, "conv_prepare: the tail is only written here when every span is one token");
     LLB_REQUIRE(T > 0 && C > 0 && src && w && span_row && span_len && span_pos && span_slot && num_spans > 0,
@@ -220,6 +228,9 @@ LLB_EXPORT int llb_conv_prepare(const void* src, int src_dtype, long long row_st
         ConvSegment& s = p.seg[i];
         s.col0 = seg_col0[i]; s.heads = seg_heads[i]; s.hd = seg_hd[i]; s.act = seg_act[i]; s.rotary_dim = seg_rotary[i];
         s.norm = seg_norm[i]; s.eps = seg_eps[i]; s.post_scale = seg_scale[i]; s.out = seg_out[i];
+        s.temp_coef = seg_temp_coef ? seg_temp_coef[i] : 0.0f;
+        s.temp_every = seg_temp_every ? seg_temp_every[i] : 0;
+        LLB_REQUIRE(s.temp_every >= 0, "conv_prepare: a temperature step of %d positions", s.temp_every);
         s.out_dtype = seg_out_dtype[i]; s.to_cache = seg_to_cache[i];
         LLB_REQUIRE(s.heads > 0 && s.hd > 0 && s.hd <= 64 * CONV_MAX_PAIRS, "conv_prepare: heads of %d; at most %d", s.hd,
                     64 * CONV_MAX_PAIRS);
@@ -236,6 +247,20 @@ LLB_EXPORT int llb_conv_prepare(const void* src, int src_dtype, long long row_st
     else if (src_dtype == LLB_BF16) conv_prepare_kernel<__nv_bfloat16><<<blocks, 128, 0, stream>>>(p);
     else return llb_fail("conv_prepare: unknown dtype %d", src_dtype);
     return llb_check_launch("conv_prepare");
+}
+
+LLB_EXPORT int llb_conv_prepare(const void* src, int src_dtype, long long row_stride, int c0, int C, int taps, int T,
+                                const float* w, const int* span_row, const int* span_len, const int* span_pos,
+                                const int* span_slot, int num_spans, float* state, long long state_stride,
+                                long long tail_off, const int* slot_mapping, const float* freq, float rot_scale,
+                                int num_segments, const int* seg_col0, const int* seg_heads, const int* seg_hd,
+                                const int* seg_act, const int* seg_rotary, const int* seg_norm, const float* seg_eps,
+                                const float* seg_scale, void* const* seg_out, const int* seg_out_dtype,
+                                const int* seg_to_cache, int fuse_tail, cudaStream_t stream) {
+    return llb_conv_prepare_temp(src, src_dtype, row_stride, c0, C, taps, T, w, span_row, span_len, span_pos, span_slot,
+                                 num_spans, state, state_stride, tail_off, slot_mapping, freq, rot_scale, num_segments,
+                                 seg_col0, seg_heads, seg_hd, seg_act, seg_rotary, seg_norm, seg_eps, seg_scale, nullptr,
+                                 nullptr, seg_out, seg_out_dtype, seg_to_cache, fuse_tail, stream);
 }
 
 // The requests' tails after this step (see the head of the file); arguments as llb_conv_prepare.

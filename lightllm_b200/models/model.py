@@ -34,9 +34,9 @@ class Model:
         # parts that rewrite the stream before a run entry (None for most)
         self.enters: List[Optional[Part]] = [build_part("stream", e.enter) if e.enter is not None else None
                                              for e in self.run]
-        mixers = [self.layers[e.layer].mixer for e in self.run]
+        # (a layer's needs: its mixer's, and what the filters on its sub-blocks' inputs keep of earlier tokens)
         self.cache_layout = CacheLayout.build(
-            [m.cache_spec() if m is not None else None for m in mixers], [e.cache_of for e in self.run])
+            [self.layers[e.layer].cache_spec() for e in self.run], [e.cache_of for e in self.run])
         self.dtype: Optional[torch.dtype] = None
         self.device: Optional[torch.device] = None
         self._prepare_hooks = None

@@ -5,7 +5,11 @@ from .block import Block, build_part
 from .conv_attention import ConvAttentionMixer
 from .delta import ChannelDeltaMixer
 from .moe import RoutedExperts
-from .stream import StreamReinjection
+from .stream import StreamReinjection, StreamStepVector
+from .input_conv import CausalInputConv
+from .mixed_heads_attention import MixedHeadsAttention
+from .matrix_memory import MatrixMemoryMixer
+from .joined_mixers import JoinedMixers
 from .embedding import LMHead, TokenEmbedding
 from .gated_attention import GatedAttentionMixer, LatentAttentionMixer
 from .mlp import GatedMLP
@@ -16,4 +20,5 @@ from .rotary import NoPositionEncoding, RotaryEmbedding
 __all__ = ["CacheView", "FeedForward", "Mixer", "Norm", "Part", "PositionEncoding", "AttentionMixer", "Block",
            "build_part", "LMHead", "TokenEmbedding", "GatedMLP", "RMSNorm", "LayerNorm", "GatedAttentionMixer",
            "LatentAttentionMixer", "RetentionMixer", "NoPositionEncoding", "RotaryEmbedding", "ConvAttentionMixer",
-           "ChannelDeltaMixer", "RoutedExperts", "StreamReinjection"]
+           "ChannelDeltaMixer", "RoutedExperts", "StreamReinjection", "StreamStepVector", "CausalInputConv",
+           "MixedHeadsAttention", "MatrixMemoryMixer", "JoinedMixers"]

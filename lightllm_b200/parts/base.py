@@ -18,6 +18,9 @@ Roles and what each must provide:
                fused rotation kernel can apply, else ``apply(q, k, positions) -> (q, k)``.
 ``embedding``  ``forward(token_ids[T] int32, ctx) -> residual[T, D] float32``.
 ``head``       ``forward(x[R, D], ctx) -> logits[R, V] float32``.
+``filter``     ``forward(h[T, D] float32, ctx, cache, out_dtype, last_reader) -> x[T, D]``: what a sub-block reads instead
+               of h; ``state_floats()`` floats of the run's state plane are its own.
+``stream``     ``forward(residual, ctx)``: rewrites the stream before a run entry.
 
 The residual stream is float32 in both precisions, so the residual sum is exact to float.
 """
@@ -95,13 +98,23 @@ class CacheView:
 
     ``k``, ``v``: ``[pages * page_size, kv_heads, head_dim]`` or ``None``; ``group`` indexes
     ``ctx.slot_mapping`` and ``ctx.block_tables``; ``state``: ``[max_seqs, *shape]`` or ``None``,
-    indexed by ``Span.slot``; ``writes`` is False when the planes belong to another run entry."""
+    indexed by ``Span.slot``; ``writes`` is False when the planes belong to another run entry.
+    ``state_offset``: where this part's floats begin inside a request's slot, when several parts of a layer share
+    the run's one state plane (a flat float32 plane; a part that is alone in its plane finds 0)."""
 
     group: Optional[int] = None
     k: Optional[torch.Tensor] = None
     v: Optional[torch.Tensor] = None
     state: Optional[torch.Tensor] = None
     writes: bool = True
+    state_offset: int = 0
+
+    def at(self, offset: int, pages: bool = True) -> "CacheView":
+        """The same planes for a part whose floats begin ``offset`` further into the slot (without the pages when
+        the part keeps none)."""
+        if pages:
+            return CacheView(self.group, self.k, self.v, self.state, self.writes, self.state_offset + offset)
+        return CacheView(None, None, None, self.state, self.writes, self.state_offset + offset)
 
 
 class Mixer(Part):
@@ -128,6 +141,19 @@ class Norm(Part):
         raise NotImplementedError
 
     def forward_rows(self, residual, rows, ctx):
+        raise NotImplementedError
+
+
+class InputFilter(Part):
+    """Rewrites what a sub-block reads (the normed stream) before the sub-block's part sees it, e.g. a causal
+    convolution over time.  ``state_floats()`` floats of the run's state plane keep what it needs of earlier tokens."""
+
+    role = "filter"
+
+    def state_floats(self) -> int:
+        return 0
+
+    def forward(self, h, ctx, cache: Optional[CacheView], out_dtype, last_reader: bool = True):
         raise NotImplementedError
 
 

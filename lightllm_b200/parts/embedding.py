@@ -56,15 +56,20 @@ class TokenEmbedding(Part):
 class LMHead(Part):
     """``logits = x @ W^T`` in float32.  ``weight_name`` is the head's own matrix, or the
     embedding table's name when the two are tied (the reference always uses the table,
-    src/engine/engine_server.cpp:1968,2042, whatever ``tie_word_embeddings`` says)."""
+    src/engine/engine_server.cpp:1968,2042, whatever ``tie_word_embeddings`` says).  ``softcap`` (a positive number):
+    ``logits <- softcap * tanh(logits / softcap)``."""
 
     graph_safe = True
 
     role = "head"
 
-    def __init__(self, prefix: str, vocab_size: int, hidden_size: int, weight_name: str = "weight"):
+    def __init__(self, prefix: str, vocab_size: int, hidden_size: int, weight_name: str = "weight",
+                 softcap: Optional[float] = None):
+        if softcap is not None and not softcap > 0:
+            raise ValueError(f"a soft cap on the logits must be positive, got {softcap}")
         self.name = f"{prefix}.{weight_name}" if prefix else weight_name
         self.vocab_size, self.hidden_size = vocab_size, hidden_size
+        self.softcap = float(softcap) if softcap is not None else None
         self.weight = None
 
     def weight_specs(self) -> List[WeightSpec]:
@@ -76,7 +81,10 @@ class LMHead(Part):
     def forward(self, x, ctx=None):
         # The norm is not folded into this contraction: with a vocabulary's worth of blocks, each would
         # repeat the norm of every row.
-        return L.linear(x, self.weight, None, L.STORE_F32)
+        logits = L.linear(x, self.weight, None, L.STORE_F32)
+        if self.softcap is not None:
+            ops.softcap(logits, self.softcap)
+        return logits
 
 
 register_part("embedding", "token_embedding", TokenEmbedding)

@@ -12,7 +12,7 @@ from .base import FeedForward, LazyNorm
 
 
 # activation name -> the kernels' code
-ACTIVATIONS = {"silu": 0, "clamped_swish": 1}
+ACTIVATIONS = {"silu": 0, "clamped_swish": 1, "gelu_tanh": 2}
 
 
 class GatedMLP(FeedForward):
@@ -20,6 +20,7 @@ class GatedMLP(FeedForward):
 
     ``silu``: SwiGLU, ``silu(g) * u`` (src/engine/engine_server.cpp:1875-1880, SiLU as src/ops/elementwise.cu:27-33).
     ``clamped_swish``: ``g' = min(g, limit)``, ``u' = clamp(u, -limit, limit)``, ``g' * sigmoid(alpha * g') * (u' + up_shift)``.
+    ``gelu_tanh``: ``0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))) * u``.
 
     The gate and up matrices are interleaved row by row at load time, so that one contraction
     produces each (gate, up) pair in adjacent columns and the epilogue writes only

@@ -35,8 +35,10 @@ class RMSNorm(Norm):
         """(weight, eps) for kernels that fold this norm into their prologue."""
         return self.weight, self.eps
 
-    def forward(self, residual, ctx=None):
-        out = torch.empty(residual.shape, dtype=self.out_dtype, device=residual.device)
+    def forward(self, residual, ctx=None, dtype=None):
+        """``dtype``: the output's dtype when it is not the compute dtype (float32 for a reader that filters the normed
+        stream before anything rounds it)."""
+        out = torch.empty(residual.shape, dtype=dtype or self.out_dtype, device=residual.device)
         ops.rmsnorm(residual, self.weight, self.eps, out)
         return out
 

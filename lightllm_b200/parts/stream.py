@@ -52,3 +52,30 @@ class StreamReinjection(Part):
 
 
 register_part("stream", "reinjection", StreamReinjection)
+
+
+class StreamStepVector(Part):
+    """``h <- h + step[index]``: a learned vector is added to every row of the stream, e.g. before every pass of a looped
+    stretch of layers.  ``step_name`` is ``[steps, hidden]`` and ``index`` picks the row; the sum is float32."""
+
+    role = "stream"
+    graph_safe = True
+
+    def __init__(self, prefix: str, hidden_size: int, step_name: str, steps: int, index: int):
+        if not 0 <= index < steps:
+            raise ValueError(f"step vector {index} of {steps}")
+        self.step_name = f"{prefix}.{step_name}" if prefix else step_name
+        self.hidden_size, self.steps, self.index = hidden_size, steps, index
+        self.step = None
+
+    def weight_specs(self) -> List[WeightSpec]:
+        return [WeightSpec(self.step_name, (self.steps, self.hidden_size), init=("normal", 0.1))]
+
+    def bind(self, tensors, dtype, device) -> None:
+        self.step = tensors[self.step_name][self.index].float().contiguous()
+
+    def forward(self, residual, ctx) -> None:
+        ops.add_row(residual, self.step)
+
+
+register_part("stream", "step_vector", StreamStepVector)
