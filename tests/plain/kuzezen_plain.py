@@ -142,12 +142,13 @@ def layer(x, i: int, cfg: dict, t) -> torch.Tensor:
         raise ValueError(spec["type"])
     eps, p = float(cfg["norm"]["eps"]), f"l{i}"
     h = rms_norm(x, t[f"{p}.norm1"], eps)
-    hm = h + causal_conv(h, t[f"{p}.canon1"])
+    taps = (cfg.get("canon") or {}).get("taps")          # no 'canon': the sub-layers read h itself
+    hm = h + causal_conv(h, t[f"{p}.canon1"]) if taps else h
     branch = parallel_mixer(hm, spec["mixer"], t, f"{p}.mix", eps)
     if spec.get("mlp") is not None:
         if spec["mlp"]["kind"] != "dense":
             raise ValueError(spec["mlp"]["kind"])
-        hf = h + causal_conv(h, t[f"{p}.canon2"])
+        hf = h + causal_conv(h, t[f"{p}.canon2"]) if taps else h
         branch = branch + dense_ff(hf, t, f"{p}.mlp")
     return x + float(cfg.get("residual_mult", 1.0)) * branch
 
