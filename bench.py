@@ -5,7 +5,7 @@
     python bench.py --sizes 1.5b|7b          (the larger sizes of the family: a line of their own)
     python bench.py [--sizes ..] --only decode|prefill [--prompt-len N]     (one part, at another context length)
     python bench.py --only small-mixed       (the steps of a loaded server: a 16-token portion beside decoded tokens)
-    python bench.py --design kudadra|bulitar [--sizes 1.5b] [--layers L]     (another design beside Qwen2 at equal sizes)
+    python bench.py --design kudadra|bulitar|kuzezen [--sizes 1.5b] [--layers L]     (another design beside Qwen2 at equal sizes)
 
 Prints one JSON line.  ``value`` is decoded tokens a second over K timed decode steps of a
 batch of 8 requests that each hold a 2,048-token prompt (random weights, random token ids),
@@ -365,6 +365,25 @@ def bulitar_config(base: dict, layers: int, kinds=("attention", "channel_delta")
             "layers": [{"type": kinds[i % len(kinds)], "mixer": mixers[kinds[i % len(kinds)]], "mlp": mlp} for i in range(n)]}
 
 
+def kuzezen_config(base: dict, layers: int, ff: bool = True) -> dict:
+    """A Kuzezen model with the width, feed-forward, head count, head size and vocabulary of a Qwen2 configuration, run as
+    ``layers`` layer runs: the first ``(layers - 1) // 2`` layers twice in a row (the loop), the one or two after them
+    once.  Every layer has both mixers, each with
+    the base's heads and head size (the attention with the base's kv heads, three taps and a temperature that steps every
+    256 positions), and four input taps; ``ff=False`` leaves the feed-forwards out."""
+    D, H, G = base["hidden_size"], base["num_attention_heads"], base["num_key_value_heads"]
+    hd = base.get("head_dim", D // H)
+    inner = max(1, (layers - 1) // 2)
+    mixer = {"left": {"heads": H, "kv_heads": G, "dim": hd, "vdim": hd, "conv": 3, "scale": hd ** -0.5,
+                      "q_temp": {"coef": 0.3, "every": 256}},
+             "right": {"heads": H, "dim": hd, "vdim": hd, "gate_cap": 15.0}}
+    mlp = {"kind": "dense", "ff": base["intermediate_size"]} if ff else None
+    return {"architecture": "Kuzezen", "vocab": base["vocab_size"], "width": D, "embedding": {"scale": 16.0},
+            "norm": {"eps": 1e-6}, "canon": {"taps": 4}, "residual_mult": 0.5, "logit_softcap": 30.0,
+            "loop": {"start": 0, "stop": inner, "times": 2},
+            "layers": [{"type": "parallel", "mixer": mixer, "mlp": mlp} for _ in range(inner + layers - 2 * inner)]}
+
+
 def run_design(name: str, sizes: str, layers: int, steps: int, warmup: int, only=None) -> int:
     """Prefill of one 2,048-token prompt and decode at batch 1 / 8 / 64 over 2,048-token contexts for another design:
     its kinds of layer in turn, each kind alone, and Qwen2 with as many layer runs of the same width, feed-forward,
@@ -379,6 +398,9 @@ def run_design(name: str, sizes: str, layers: int, steps: int, warmup: int, only
         for kind in ("attention", "channel_delta"):
             arms[f"bulitar/{kind}"] = bulitar_config(base, layers, (kind,))
         arms["bulitar/every expert chosen"] = bulitar_config(base, layers, experts=2, top=2)
+    elif name == "kuzezen":
+        arms = {"qwen2": base, "kuzezen": kuzezen_config(base, layers),
+                "kuzezen/no feed-forward": kuzezen_config(base, layers, ff=False)}
     else:
         arms = {"qwen2": base, "kudadra": kudadra_config(base, layers)}
     for kind in ("latent_attention", "attention", "retention") if name == "kudadra" else ():
@@ -419,7 +441,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=QWEN25_05B["num_hidden_layers"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (for profiling runs)")
-    ap.add_argument("--design", choices=["kudadra", "bulitar"], default=None,
+    ap.add_argument("--design", choices=["kudadra", "bulitar", "kuzezen"], default=None,
                     help="measure another design beside Qwen2 at equal sizes (0.5B sizes, or --sizes; --layers, default 6; "
                          "--only names arms, e.g. kudadra,qwen2): a line of its own, not the bench record")
     ap.add_argument("--sizes", choices=["1.5b", "7b"], default=None,
