@@ -42,7 +42,18 @@ struct DecodeParams {
     float* part_acc;               // [tiles, Hkv, nsplit, G, HD]
     float* part_ml;                // [tiles, Hkv, nsplit, G, 2]   (m in base-2 units, l)
     const float* sinks;            // [Hq] or null: exp(sinks[h]) joins head h's softmax denominator once
+    // Crossed values (cross > 1, = Hkv): every query head's weights are applied to the values of EVERY kv head.  grid.y
+    // then counts (kv head of the keys, kv head of the values) pairs, out is [T, Hq, cross, HD], and the partial results
+    // are laid out by pair.  out_f32, when given, takes the place of `out` (crossed or not).
+    int cross;
+    float* out_f32;
 };
+// Where head `head`'s result over the values of kv head `vh` goes, dimension d of row `row`.
+__device__ __forceinline__ void store_out(const DecodeParams& p, int HD, int row, int head, int vh, int d, float v) {
+    const int col = p.cross > 1 ? head * p.cross + vh : head;
+    if (p.out_f32) p.out_f32[((size_t)row * p.Hq * p.cross + col) * HD + d] = v;
+    else p.out[((size_t)row * p.Hq * p.cross + col) * HD + d] = __float2bfloat16_rn(v);
+}
 
 // What a sink adds to a denominator whose terms are 2^(s - M): exp(sink) = 2^(sink * log2 e).
 __device__ __forceinline__ float sink_term(const float* sinks, int head, float M) {
@@ -85,7 +96,9 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_decode_mma_kernel(DecodePar
     // per warp: K[NST], V[NST]; afterwards reused for the merge of the warps
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t wbase = smem_addr(smem) + warp * 2 * NST * TILE_BYTES;
-    const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int tile = blockIdx.x, split = blockIdx.z;
+    const int kvh = p.cross > 1 ? blockIdx.y / p.cross : blockIdx.y;          // the keys' head
+    const int vh = p.cross > 1 ? blockIdx.y % p.cross : kvh;                  // the values' head
     const int G = p.Hq / p.Hkv;
 
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -145,9 +158,9 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_decode_mma_kernel(DecodePar
             const int row = idx / CH, ch = idx % CH;
             const int s = __shfl_sync(0xffffffffu, slot, row);
             const bool valid = s >= 0;
-            const size_t off = (size_t)(valid ? s : 0) * row_stride + (size_t)(kvh * HD + ch * 8);
-            cp_async16(tile_addr<HD>(kbase, row, ch), p.k_cache + off, valid);
-            cp_async16(tile_addr<HD>(vbase, row, ch), p.v_cache + off, valid);
+            const size_t off = (size_t)(valid ? s : 0) * row_stride + (size_t)(ch * 8);
+            cp_async16(tile_addr<HD>(kbase, row, ch), p.k_cache + off + kvh * HD, valid);
+            cp_async16(tile_addr<HD>(vbase, row, ch), p.v_cache + off + vh * HD, valid);
         }
         cp_async_commit();
     };
@@ -267,7 +280,7 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_decode_mma_kernel(DecodePar
         }
     }
     __syncthreads();
-    const size_t base = (((size_t)tile * p.Hkv + kvh) * p.nsplit + split) * G;
+    const size_t base = (((size_t)tile * gridDim.y + blockIdx.y) * p.nsplit + split) * G;
     for (int i = threadIdx.x; i < G * HD; i += blockDim.x) {
         const int g = i / HD, d = i - g * HD;
         float M = -INFINITY;
@@ -292,7 +305,7 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_decode_mma_kernel(DecodePar
             }
         } else if (p.nsplit == 1) {
             L += sink_term(p.sinks, kvh * G + g, M);
-            p.out[((size_t)row0 * p.Hq + kvh * G + g) * HD + d] = __float2bfloat16_rn(a / L);
+            store_out(p, HD, row0, kvh * G + g, vh, d, a / L);
         } else {
             p.part_acc[(base + g) * HD + d] = a;
             if (d == 0) {
@@ -322,7 +335,7 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_decode_mma_kernel(DecodePar
                 }
             }
             L += sink_term(p.sinks, kvh * G + g, M);
-            p.out[((size_t)row0 * p.Hq + kvh * G + g) * HD + d] = __float2bfloat16_rn(a / L);
+            store_out(p, HD, row0, kvh * G + g, vh, d, a / L);
         }
         cluster_sync_all();        // no block leaves while another may still read its shared memory
     }
@@ -331,13 +344,16 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_decode_mma_kernel(DecodePar
 // out = sum_s 2^(m_s - M) acc_s / sum_s 2^(m_s - M) l_s; one warp per (tile, head).
 __global__ void __launch_bounds__(32) decode_merge_kernel(DecodeParams p, int HD) {
     __shared__ float wsm[MERGE_MAX_SPLITS];
-    const int tile = blockIdx.x, head = blockIdx.y, lane = threadIdx.x;
+    // blockIdx.y: the query head, or with crossed values (query head, values' kv head)
+    const int tile = blockIdx.x, head = p.cross > 1 ? blockIdx.y / p.cross : blockIdx.y, lane = threadIdx.x;
     const int G = p.Hq / p.Hkv;
     const int kvh = head / G, g = head - kvh * G;
+    const int vh = p.cross > 1 ? blockIdx.y % p.cross : kvh;
+    const int pair = p.cross > 1 ? kvh * p.cross + vh : kvh, pairs = p.cross > 1 ? p.Hkv * p.cross : p.Hkv;
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int span = p.tile_span[tile];
     const int row0 = p.span_row[span] + p.tile_q0[tile];
-    const size_t base0 = ((size_t)tile * p.Hkv + kvh) * p.nsplit;
+    const size_t base0 = ((size_t)tile * pairs + pair) * p.nsplit;
     asm volatile("griddepcontrol.wait;" ::: "memory");
     float M = -INFINITY;
     for (int s = lane; s < p.nsplit; s += 32) M = fmaxf(M, p.part_ml[((base0 + s) * G + g) * 2]);
@@ -357,7 +373,7 @@ __global__ void __launch_bounds__(32) decode_merge_kernel(DecodeParams p, int HD
         float a = 0.0f;
 #pragma unroll 8
         for (int s = 0; s < p.nsplit; ++s) a = fmaf(wsm[s], p.part_acc[((base0 + s) * G + g) * HD + d], a);
-        p.out[((size_t)row0 * p.Hq + head) * HD + d] = __float2bfloat16_rn(a * inv);
+        store_out(p, HD, row0, head, vh, d, a * inv);
     }
 }
 
@@ -438,16 +454,16 @@ struct Launcher {
         const bool cluster = p.nsplit > 1 && p.nsplit <= CLUSTER_MAX_SPLITS;
         cudaError_t e;
         if (cluster)
-            e = launch_pdl_cluster(paged_decode_mma_kernel<HD, true, BK, NST>, dim3(num_tiles, p.Hkv, p.nsplit), dim3(NWARPS * 32),
+            e = launch_pdl_cluster(paged_decode_mma_kernel<HD, true, BK, NST>, dim3(num_tiles, p.Hkv * p.cross, p.nsplit), dim3(NWARPS * 32),
                                    smem, stream, p);
         else
-            e = launch_pdl(paged_decode_mma_kernel<HD, false, BK, NST>, dim3(num_tiles, p.Hkv, p.nsplit), dim3(NWARPS * 32), smem,
+            e = launch_pdl(paged_decode_mma_kernel<HD, false, BK, NST>, dim3(num_tiles, p.Hkv * p.cross, p.nsplit), dim3(NWARPS * 32), smem,
                            stream, p);
         if (e != cudaSuccess) return llb_fail("decode attention: launch failed: %s", cudaGetErrorString(e));
         rc = llb_check_launch("paged_decode_mma");
         if (rc) return rc;
         if (p.nsplit > 1 && !cluster) {
-            e = launch_pdl(decode_merge_kernel, dim3(num_tiles, p.Hq), dim3(32), 0, stream, p, HD);
+            e = launch_pdl(decode_merge_kernel, dim3(num_tiles, p.Hq * p.cross), dim3(32), 0, stream, p, HD);
             if (e != cudaSuccess) return llb_fail("decode merge: launch failed: %s", cudaGetErrorString(e));
             rc = llb_check_launch("decode_merge");
         }
@@ -487,17 +503,21 @@ LLB_EXPORT int llb_paged_decode_mma_cluster_splits() { return CLUSTER_MAX_SPLITS
 // nsplit * (hd + 2) floats when nsplit > llb_paged_decode_mma_cluster_splits() (fewer splits merge inside the kernel).
 // sinks [Hq] float or null: exp(sinks[h]) is added once to head h's softmax denominator.  v_cache may be k_cache
 // (values read out of the key rows).
-LLB_EXPORT int llb_paged_decode_mma_sinks(const void* q, const void* k_cache, const void* v_cache, void* out,
+// cross > 1 (then = Hkv, and no sinks): crossed values, out is [T, Hq, cross, hd] and holds every query head's
+// weights applied to the values of every kv head; scratch counts Hq * cross heads.  out_float: out is float, not bf16.
+LLB_EXPORT int llb_paged_decode_mma_cross(const void* q, const void* k_cache, const void* v_cache, void* out,
                                           const int* tile_span, const int* tile_q0, int num_tiles, const int* span_row,
                                           const int* span_pos, const int* block_table, int max_pages, int page_size,
                                           int Hq, int Hkv, int hd, int window, float scale, int nsplit, float* scratch,
-                                          const float* sinks, cudaStream_t stream) {
+                                          const float* sinks, int cross, int out_float, cudaStream_t stream) {
     if (num_tiles == 0) return 0;
+    LLB_REQUIRE(cross == 1 || (cross == Hkv && sinks == nullptr),
+                "decode attention: crossed values take cross = the number of kv heads (%d), got %d, and no sinks", Hkv, cross);
     LLB_REQUIRE(llb_paged_decode_mma_supports(Hq, Hkv, hd), "decode attention: %d/%d heads of size %d are not supported "
                 "(groups of at most 16, head size 64 or 128)", Hq, Hkv, hd);
     LLB_REQUIRE(nsplit >= 1 && nsplit <= MERGE_MAX_SPLITS && (nsplit <= CLUSTER_MAX_SPLITS || scratch != nullptr),
                 "decode attention: split count %d is outside 1..%d or scratch is missing", nsplit, MERGE_MAX_SPLITS);
-    LLB_REQUIRE(page_size > 0 && max_pages > 0 && Hkv <= 65535, "decode attention: bad sizes");
+    LLB_REQUIRE(page_size > 0 && max_pages > 0 && Hkv * cross <= 65535 && Hq * cross <= 65535, "decode attention: bad sizes");
     LLB_REQUIRE(((uintptr_t)q % 16 == 0) && ((uintptr_t)k_cache % 16 == 0) && ((uintptr_t)v_cache % 16 == 0),
                 "decode attention: tensors must be 16-byte aligned");
     DecodeParams p;
@@ -506,11 +526,23 @@ LLB_EXPORT int llb_paged_decode_mma_sinks(const void* q, const void* k_cache, co
     p.block_table = block_table; p.max_pages = max_pages; p.page_size = page_size; p.Hq = Hq; p.Hkv = Hkv;
     p.window = window; p.nsplit = nsplit; p.scale_log2e = scale * 1.4426950408889634f;
     p.sinks = sinks;
+    p.cross = cross;
+    p.out_f32 = out_float ? (float*)out : nullptr;
     const int G = Hq / Hkv;
     p.part_acc = scratch;
-    p.part_ml = scratch ? scratch + (size_t)num_tiles * Hkv * nsplit * G * hd : nullptr;
+    p.part_ml = scratch ? scratch + (size_t)num_tiles * Hkv * cross * nsplit * G * hd : nullptr;
     if (hd == 64) return launch<64>(p, num_tiles, stream);
     return launch<128>(p, num_tiles, stream);
+}
+
+LLB_EXPORT int llb_paged_decode_mma_sinks(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                          const int* tile_span, const int* tile_q0, int num_tiles, const int* span_row,
+                                          const int* span_pos, const int* block_table, int max_pages, int page_size,
+                                          int Hq, int Hkv, int hd, int window, float scale, int nsplit, float* scratch,
+                                          const float* sinks, cudaStream_t stream) {
+    return llb_paged_decode_mma_cross(q, k_cache, v_cache, out, tile_span, tile_q0, num_tiles, span_row, span_pos,
+                                      block_table, max_pages, page_size, Hq, Hkv, hd, window, scale, nsplit, scratch,
+                                      sinks, 1, 0, stream);
 }
 
 LLB_EXPORT int llb_paged_decode_mma(const void* q, const void* k_cache, const void* v_cache, void* out,

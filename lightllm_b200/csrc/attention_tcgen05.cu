@@ -117,16 +117,23 @@ struct AttnTcParams {
     float* part_ml;            // [parts, Hq, 128, 2]  (m in base-2 units, l)
     int* error_flag;
     const float* sinks;        // [Hq] or null: exp(sinks[h]) joins head h's softmax denominator once
+    // Crossed values (cross > 1, = Hkv): every query head's weights are applied to the values of EVERY kv head.  The
+    // items then count cross "heads" per query head, head * cross + (kv head of the values); partial results are laid
+    // out by these, and out_f32 [T, Hq, cross, HD] (float) takes the place of `out`.
+    int cross;
+    float* out_f32;
 };
 
 // What one work item is: 128 query rows of one span and one head over a range of key tiles.
 struct Item {
     int head, span, row0, nrows, pos0, hi, lo, kt0, ntiles, part;
+    int qhead;      // the query head; `head` is where the result goes (the same unless values are crossed)
 };
 __device__ __forceinline__ Item make_item(const AttnTcParams& p, int idx) {
     Item it;
-    const int tile = idx / p.Hq;
-    it.head = idx - tile * p.Hq;
+    const int tile = idx / (p.Hq * p.cross);
+    it.head = idx - tile * (p.Hq * p.cross);
+    it.qhead = it.head / p.cross;
     it.span = p.tile_span[tile];
     const int q0 = p.tile_q0[tile];
     it.row0 = p.span_row[it.span] + q0;
@@ -234,14 +241,15 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             if (idx >= total) continue;
             const Item it = make_item(p, idx);
             if (it.ntiles <= 0) continue;        // cannot happen with the lists the engine makes; every role skips it alike
-            const int kvh = it.head / group;
+            const int kvh = it.qhead / group;                                   // the keys' head
+            const int vh = p.cross > 1 ? it.head - it.qhead * p.cross : kvh;    // the values' head
             const int* bt = p.block_table + (size_t)it.span * p.max_pages;
             if (n_item > 0) ok = mbar_wait(bar_q_free, (n_item - 1) & 1, abort_flag) && ok;
             if (lane == 0 && ok) {
                 mbar_expect_tx(bar_q_full, KB * TILE_BYTES);
 #pragma unroll
                 for (int kb = 0; kb < KB; ++kb)
-                    tma_load_2d(q_s + kb * TILE_BYTES, &map_q, it.head * HD + kb * 64, it.row0, bar_q_full);
+                    tma_load_2d(q_s + kb * TILE_BYTES, &map_q, it.qhead * HD + kb * 64, it.row0, bar_q_full);
             }
             for (int j = 0; j < it.ntiles; ++j, ++n_kv) {
                 const int st = n_kv & 1;
@@ -262,7 +270,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 #pragma unroll
                     for (int kb = 0; kb < KB; ++kb) {
                         tma_load_2d(k_s + (st * KB + kb) * TILE_BYTES + off, &map_k, kvh * HD + kb * 64, y, &bar_kv_full[st]);
-                        tma_load_2d(v_s + (st * KB + kb) * TILE_BYTES + off, &map_v, kvh * HD + kb * 64, y, &bar_kv_full[st]);
+                        tma_load_2d(v_s + (st * KB + kb) * TILE_BYTES + off, &map_v, vh * HD + kb * 64, y, &bar_kv_full[st]);
                     }
                 }
                 __syncwarp();
@@ -417,29 +425,37 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             named_barrier(BAR_SOFTMAX, NUM_SOFTMAX);
             const float l_row = lx[r] + lx[BQ + r];
             if (ok && r < it.nrows && it.part >= 0) {
-                float* po = p.part_o + (((size_t)it.part * p.Hq + it.head) * BQ + r) * HD + half * HO;
+                float* po = p.part_o + (((size_t)it.part * p.Hq * p.cross + it.head) * BQ + r) * HD + half * HO;
 #pragma unroll
                 for (int d = 0; d < HO; d += 4)
                     *reinterpret_cast<float4*>(po + d) = make_float4(o[d], o[d + 1], o[d + 2], o[d + 3]);
                 if (half == 0) {
-                    float* pm = p.part_ml + (((size_t)it.part * p.Hq + it.head) * BQ + r) * 2;
+                    float* pm = p.part_ml + (((size_t)it.part * p.Hq * p.cross + it.head) * BQ + r) * 2;
                     pm[0] = m_run;
                     pm[1] = l_row;
                 }
             } else if (ok && r < it.nrows) {
                 // a sink is one more term of the denominator, 2^(sink * log2 e - m), without a value
-                const float sink = p.sinks ? exp2f(p.sinks[it.head] * 1.4426950408889634f - m_run) : 0.0f;
+                const float sink = p.sinks ? exp2f(p.sinks[it.qhead] * 1.4426950408889634f - m_run) : 0.0f;
                 const float inv = 1.0f / (l_row + sink);
-                __nv_bfloat16* dst = p.out + ((size_t)(it.row0 + r) * p.Hq + it.head) * HD + half * HO;
+                if (p.out_f32) {
+                    float* dst = p.out_f32 + ((size_t)(it.row0 + r) * p.Hq * p.cross + it.head) * HD + half * HO;
 #pragma unroll
-                for (int d = 0; d < HO; d += 8) {
-                    uint32_t w[4];
+                    for (int d = 0; d < HO; d += 4)
+                        *reinterpret_cast<float4*>(dst + d) =
+                            make_float4(o[d] * inv, o[d + 1] * inv, o[d + 2] * inv, o[d + 3] * inv);
+                } else {
+                    __nv_bfloat16* dst = p.out + ((size_t)(it.row0 + r) * p.Hq * p.cross + it.head) * HD + half * HO;
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const __nv_bfloat162 h = __floats2bfloat162_rn(o[d + 2 * e] * inv, o[d + 2 * e + 1] * inv);
-                        w[e] = *reinterpret_cast<const uint32_t*>(&h);
+                    for (int d = 0; d < HO; d += 8) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const __nv_bfloat162 h = __floats2bfloat162_rn(o[d + 2 * e] * inv, o[d + 2 * e + 1] * inv);
+                            w[e] = *reinterpret_cast<const uint32_t*>(&h);
+                        }
+                        *reinterpret_cast<uint4*>(dst + d) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
-                    *reinterpret_cast<uint4*>(dst + d) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
             }
             ++n_item;
@@ -467,7 +483,9 @@ struct MergeParams {
     const float* part_o;
     const float* part_ml;
     const float* sinks;
-    int Hq, HD;
+    int Hq, HD;                // Hq counts the heads of the parts' layout (query heads x cross)
+    int cross;
+    float* out_f32;            // takes the place of out when given
 };
 
 __global__ void __launch_bounds__(256) attention_tcgen05_merge_kernel(MergeParams p) {
@@ -497,8 +515,13 @@ __global__ void __launch_bounds__(256) attention_tcgen05_merge_kernel(MergeParam
             const float4 a = *reinterpret_cast<const float4*>(p.part_o + base * HD + d);
             acc.x += w * a.x; acc.y += w * a.y; acc.z += w * a.z; acc.w += w * a.w;
         }
-        if (p.sinks) L += exp2f(p.sinks[head] * 1.4426950408889634f - M);
+        if (p.sinks) L += exp2f(p.sinks[head / p.cross] * 1.4426950408889634f - M);
         const float inv = 1.0f / L;
+        if (p.out_f32) {
+            *reinterpret_cast<float4*>(p.out_f32 + ((size_t)(p.span_row[span] + q0 + r) * p.Hq + head) * HD + d) =
+                make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+            continue;
+        }
         __nv_bfloat16* dst = p.out + ((size_t)(p.span_row[span] + q0 + r) * p.Hq + head) * HD + d;
         const __nv_bfloat162 h0 = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
         const __nv_bfloat162 h1 = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
@@ -539,7 +562,7 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
     }
     AttnTcParams pp = p;
     pp.dynamic_smem_bytes = (uint32_t)smem;
-    pp.num_items = num_tiles * p.Hq;
+    pp.num_items = num_tiles * p.Hq * p.cross;
     const int resident = (HD <= 64 ? 2 : 1) * num_sms;       // persistent blocks: as many as stay on the device
     const int grid = pp.num_items < resident ? pp.num_items : resident;
     cudaLaunchConfig_t cfg = {};
@@ -571,21 +594,25 @@ LLB_EXPORT int llb_attention_tcgen05_supports(int hd, int page_size) {
 // part_scratch (num_parts * Hq * 128 * (hd + 2) floats) for llb_attention_tcgen05_merge.
 // sinks [Hq] float or null: exp(sinks[h]) is added once to head h's softmax denominator (by the kernel for whole
 // tiles, by the merge for cut ones: give the merge the same pointer).  v_cache may be k_cache.
-LLB_EXPORT int llb_paged_attention_tcgen05_sinks(const void* q, const void* k_cache, const void* v_cache, void* out, int T,
+// cross > 1 (then = Hkv, and no sinks): crossed values.  out is float [T, Hq, cross, hd] and holds every query head's
+// weights applied to the values of every kv head; part_scratch and the merge count Hq * cross heads.
+LLB_EXPORT int llb_paged_attention_tcgen05_cross(const void* q, const void* k_cache, const void* v_cache, void* out, int T,
                                                  const int* tile_span, const int* tile_q0, int num_tiles,
                                                  const int* span_row, const int* span_len, const int* span_pos,
                                                  const int* block_table, int max_pages, int page_size, int num_slots,
                                                  int Hq, int Hkv, int hd, int window, float scale, const int* tile_k0,
                                                  const int* tile_nk, const int* tile_part, float* part_scratch,
-                                                 int num_parts, const float* sinks, int* error_flag,
-                                                 cudaStream_t stream) {
+                                                 int num_parts, const float* sinks, int cross, int out_float,
+                                                 int* error_flag, cudaStream_t stream) {
     if (num_tiles == 0) return 0;
+    LLB_REQUIRE(cross == 1 || (cross == Hkv && sinks == nullptr),
+                "attention_tcgen05: crossed values take cross = the number of kv heads (%d), got %d, and no sinks", Hkv, cross);
     LLB_REQUIRE(tile_part == nullptr || (tile_k0 && tile_nk && (num_parts == 0 || part_scratch)),
                 "attention_tcgen05: a cut key range needs tile_k0, tile_nk, tile_part and scratch");
     LLB_REQUIRE(llb_attention_tcgen05_supports(hd, page_size),
                 "attention_tcgen05: head_dim %d with page size %d is not supported (head 64 or 128; page size a "
                 "multiple of 8 that divides 128)", hd, page_size);
-    LLB_REQUIRE(Hq > 0 && Hkv > 0 && Hq % Hkv == 0 && Hq <= 65535 && (long long)num_tiles * Hq < (1ll << 30), "attention_tcgen05: bad head counts %d/%d", Hq, Hkv);
+    LLB_REQUIRE(Hq > 0 && Hkv > 0 && Hq % Hkv == 0 && (long long)Hq * cross <= 65535 && (long long)num_tiles * Hq * cross < (1ll << 30), "attention_tcgen05: bad head counts %d/%d", Hq, Hkv);
     LLB_REQUIRE(((uintptr_t)q % 16 == 0) && ((uintptr_t)k_cache % 16 == 0) && ((uintptr_t)v_cache % 16 == 0) &&
                 ((uintptr_t)out % 16 == 0), "attention_tcgen05: tensors must be 16-byte aligned");
     CUtensorMap mq, mk, mv;
@@ -595,15 +622,31 @@ LLB_EXPORT int llb_paged_attention_tcgen05_sinks(const void* q, const void* k_ca
     if ((rc = make_map(v_cache, num_slots, (long long)Hkv * hd, page_size, &mv))) return rc;
     AttnTcParams p;
     p.out = (__nv_bfloat16*)out;
+    p.cross = cross;
+    p.out_f32 = out_float ? (float*)out : nullptr;
     p.tile_span = tile_span; p.tile_q0 = tile_q0; p.span_row = span_row; p.span_len = span_len; p.span_pos = span_pos;
     p.block_table = block_table; p.max_pages = max_pages; p.page_size = page_size; p.Hq = Hq; p.Hkv = Hkv;
     p.window = window; p.num_slots = num_slots; p.scale_log2e = scale * 1.4426950408889634f; p.error_flag = error_flag;
     p.tile_k0 = tile_k0; p.tile_nk = tile_nk; p.tile_part = tile_part;
     p.sinks = sinks;
     p.part_o = part_scratch;
-    p.part_ml = part_scratch ? part_scratch + (size_t)num_parts * Hq * BQ * hd : nullptr;
+    p.part_ml = part_scratch ? part_scratch + (size_t)num_parts * Hq * cross * BQ * hd : nullptr;
     if (hd == 64) return launch<64>(mq, mk, mv, p, num_tiles, stream);
     return launch<128>(mq, mk, mv, p, num_tiles, stream);
+}
+
+LLB_EXPORT int llb_paged_attention_tcgen05_sinks(const void* q, const void* k_cache, const void* v_cache, void* out, int T,
+                                                 const int* tile_span, const int* tile_q0, int num_tiles,
+                                                 const int* span_row, const int* span_len, const int* span_pos,
+                                                 const int* block_table, int max_pages, int page_size, int num_slots,
+                                                 int Hq, int Hkv, int hd, int window, float scale, const int* tile_k0,
+                                                 const int* tile_nk, const int* tile_part, float* part_scratch,
+                                                 int num_parts, const float* sinks, int* error_flag,
+                                                 cudaStream_t stream) {
+    return llb_paged_attention_tcgen05_cross(q, k_cache, v_cache, out, T, tile_span, tile_q0, num_tiles, span_row, span_len,
+                                             span_pos, block_table, max_pages, page_size, num_slots, Hq, Hkv, hd, window,
+                                             scale, tile_k0, tile_nk, tile_part, part_scratch, num_parts, sinks, 1, 0,
+                                             error_flag, stream);
 }
 
 LLB_EXPORT int llb_paged_attention_tcgen05(const void* q, const void* k_cache, const void* v_cache, void* out, int T,
@@ -621,11 +664,15 @@ LLB_EXPORT int llb_paged_attention_tcgen05(const void* q, const void* k_cache, c
 
 // Merges the partial results of cut tiles: merge_span, merge_q0, merge_first, merge_count [num_merge] name each
 // query tile, its first part and its number of parts.
-LLB_EXPORT int llb_attention_tcgen05_merge_sinks(void* out, const int* merge_span, const int* merge_q0,
+// cross > 1: Hq still counts query heads; the parts hold Hq * cross heads and out is float [T, Hq, cross, hd].
+LLB_EXPORT int llb_attention_tcgen05_merge_cross(void* out, const int* merge_span, const int* merge_q0,
                                                  const int* merge_first, const int* merge_count, int num_merge,
                                                  const int* span_row, const int* span_len, const float* part_scratch,
-                                                 int num_parts, int Hq, int hd, const float* sinks, cudaStream_t stream) {
+                                                 int num_parts, int Hq, int hd, const float* sinks, int cross,
+                                                 int out_float, cudaStream_t stream) {
     if (num_merge == 0) return 0;
+    LLB_REQUIRE(cross >= 1 && (long long)Hq * cross <= 65535, "attention_tcgen05_merge: bad cross %d", cross);
+    Hq *= cross;
     LLB_REQUIRE(num_merge > 0 && part_scratch && num_parts > 0 && Hq > 0 && Hq <= 65535 && hd % 8 == 0,
                 "attention_tcgen05_merge: bad arguments");
     MergeParams p;
@@ -633,6 +680,8 @@ LLB_EXPORT int llb_attention_tcgen05_merge_sinks(void* out, const int* merge_spa
     p.merge_count = merge_count; p.span_row = span_row; p.span_len = span_len; p.part_o = part_scratch;
     p.part_ml = part_scratch + (size_t)num_parts * Hq * BQ * hd; p.Hq = Hq; p.HD = hd;
     p.sinks = sinks;
+    p.cross = cross;
+    p.out_f32 = out_float ? (float*)out : nullptr;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(num_merge, Hq, BQ / (256 / (hd / 4)));
     cfg.blockDim = dim3(256);
@@ -645,6 +694,14 @@ LLB_EXPORT int llb_attention_tcgen05_merge_sinks(void* out, const int* merge_spa
     cudaError_t e = cudaLaunchKernelEx(&cfg, attention_tcgen05_merge_kernel, p);
     if (e != cudaSuccess) return llb_fail("attention_tcgen05_merge: launch failed: %s", cudaGetErrorString(e));
     return llb_check_launch("attention_tcgen05_merge");
+}
+
+LLB_EXPORT int llb_attention_tcgen05_merge_sinks(void* out, const int* merge_span, const int* merge_q0,
+                                                 const int* merge_first, const int* merge_count, int num_merge,
+                                                 const int* span_row, const int* span_len, const float* part_scratch,
+                                                 int num_parts, int Hq, int hd, const float* sinks, cudaStream_t stream) {
+    return llb_attention_tcgen05_merge_cross(out, merge_span, merge_q0, merge_first, merge_count, num_merge, span_row,
+                                             span_len, part_scratch, num_parts, Hq, hd, sinks, 1, 0, stream);
 }
 
 LLB_EXPORT int llb_attention_tcgen05_merge(void* out, const int* merge_span, const int* merge_q0, const int* merge_first,

@@ -876,17 +876,22 @@ def paged_attention_tcgen05(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
                             span_row: torch.Tensor, span_len: torch.Tensor, span_pos: torch.Tensor,
                             block_table: torch.Tensor, max_pages: int, page_size: int,
                             num_heads: int, num_kv_heads: int, head_dim: int, window: int, scale: float,
-                            cut=None, sinks: Optional[torch.Tensor] = None) -> None:
+                            cut=None, sinks: Optional[torch.Tensor] = None, cross: int = 1) -> None:
     """Tensor-core attention of the listed tiles (128 query rows each) over the requests' pages; bf16.
     ``sinks`` float32 [num_heads]: ``exp(sinks[h])`` joins head h's softmax denominator once; ``v_cache`` may be
-    ``k_cache`` itself (values read out of the key rows).
+    ``k_cache`` itself (values read out of the key rows).  ``cross`` = ``num_kv_heads`` (> 1): crossed values, ``out``
+    is [T, num_heads, cross, head_dim] and holds every query head's weights applied to the values of every kv
+    head; ``cut`` must then have been made for ``num_heads * cross`` heads.  ``out`` may be float32.
 
     ``cut`` = ``(tile_k0, tile_nk, tile_part, num_parts, merge_span, merge_q0, merge_first, merge_count,
     num_merge)`` cuts long key ranges into items (see ``StepContext.attention_items``); the partial results
     are merged by a second kernel."""
-    for t in (q, k_cache, v_cache, out):
+    for t in (q, k_cache, v_cache):
         if t.dtype != torch.bfloat16:
             raise KernelError("attention_tcgen05 takes bfloat16 tensors")
+    if out.dtype not in (torch.bfloat16, torch.float32) or out.numel() != q.shape[0] * num_heads * cross * head_dim:
+        raise KernelError("attention_tcgen05: out is bfloat16 or float32 [T, heads, cross, head_dim]")
+    out_float = 1 if out.dtype == torch.float32 else 0
     T = q.shape[0]
     num_slots = k_cache.shape[0]
     k0 = nk = part = scratch = None
@@ -894,21 +899,22 @@ def paged_attention_tcgen05(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
     if cut is not None:
         k0, nk, part, num_parts = cut[0], cut[1], cut[2], cut[3]
         if num_parts:
-            scratch = torch.empty(num_parts * num_heads * 128 * (head_dim + 2), dtype=torch.float32, device=q.device)
+            scratch = torch.empty(num_parts * num_heads * cross * 128 * (head_dim + 2), dtype=torch.float32,
+                                  device=q.device)
     if sinks is not None and (sinks.dtype != torch.float32 or sinks.numel() != num_heads):
         raise KernelError(f"attention_tcgen05: sinks must be float32 [{num_heads}]")
-    _check(lib().llb_paged_attention_tcgen05_sinks(
+    _check(lib().llb_paged_attention_tcgen05_cross(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), T,
         _i32(tile_span, "tile_span"), _i32(tile_q0, "tile_q0"), num_tiles,
         _i32(span_row, "span_row"), _i32(span_len, "span_len"), _i32(span_pos, "span_pos"),
         _i32(block_table, "block_table"), max_pages, page_size, num_slots, num_heads, num_kv_heads, head_dim,
         window, ctypes.c_float(scale), _i32(k0, "tile_k0"), _i32(nk, "tile_nk"), _i32(part, "tile_part"),
-        _ptr(scratch), num_parts, _ptr(sinks), _ptr(async_error_flag(q.device)), _stream()))
+        _ptr(scratch), num_parts, _ptr(sinks), cross, out_float, _ptr(async_error_flag(q.device)), _stream()))
     if cut is not None and num_parts:
-        _check(lib().llb_attention_tcgen05_merge_sinks(
+        _check(lib().llb_attention_tcgen05_merge_cross(
             _ptr(out), _i32(cut[4], "merge_span"), _i32(cut[5], "merge_q0"), _i32(cut[6], "merge_first"),
             _i32(cut[7], "merge_count"), cut[8], _i32(span_row, "span_row"), _i32(span_len, "span_len"),
-            _ptr(scratch), num_parts, num_heads, head_dim, _ptr(sinks), _stream()))
+            _ptr(scratch), num_parts, num_heads, head_dim, _ptr(sinks), cross, out_float, _stream()))
 
 
 def paged_decode_mma_supports(num_heads: int, num_kv_heads: int, head_dim: int) -> bool:
@@ -946,24 +952,27 @@ def paged_decode_mma(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
                      span_pos: torch.Tensor, block_table: torch.Tensor, max_pages: int, page_size: int,
                      num_heads: int, num_kv_heads: int, head_dim: int, window: int, scale: float,
                      nsplit: int = 1, scratch: Optional[torch.Tensor] = None,
-                     sinks: Optional[torch.Tensor] = None) -> None:
+                     sinks: Optional[torch.Tensor] = None, cross: int = 1) -> None:
     """Tensor-core decode attention: one query row per tile over its request's pages; bf16.  ``nsplit`` cuts
     each request's keys; up to :func:`decode_mma_cluster_splits` the pieces are merged inside the kernel.
-    ``sinks`` and ``v_cache is k_cache`` as :func:`paged_attention_tcgen05`."""
+    ``sinks``, ``v_cache is k_cache``, ``cross`` (crossed values) and a float32 ``out`` as
+    :func:`paged_attention_tcgen05`."""
     if sinks is not None and (sinks.dtype != torch.float32 or sinks.numel() != num_heads):
         raise KernelError(f"decode attention: sinks must be float32 [{num_heads}]")
-    for t in (q, k_cache, v_cache, out):
+    for t in (q, k_cache, v_cache):
         if t.dtype != torch.bfloat16:
             raise KernelError("paged_decode_mma takes bfloat16 tensors")
+    if out.dtype not in (torch.bfloat16, torch.float32) or out.numel() != q.shape[0] * num_heads * cross * head_dim:
+        raise KernelError("decode attention: out is bfloat16 or float32 [T, heads, cross, head_dim]")
     if nsplit > decode_mma_cluster_splits():
-        need = attention_scratch_floats(num_tiles, num_heads, head_dim, 1, nsplit)
+        need = attention_scratch_floats(num_tiles, num_heads * cross, head_dim, 1, nsplit)
         if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need:
             raise KernelError(f"decode attention: nsplit={nsplit} needs {need} floats of scratch")
-    _check(lib().llb_paged_decode_mma_sinks(
+    _check(lib().llb_paged_decode_mma_cross(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _i32(tile_span, "tile_span"), _i32(tile_q0, "tile_q0"),
         num_tiles, _i32(span_row, "span_row"), _i32(span_pos, "span_pos"), _i32(block_table, "block_table"),
         max_pages, page_size, num_heads, num_kv_heads, head_dim, window, ctypes.c_float(scale), nsplit,
-        _ptr(scratch), _ptr(sinks), _stream()))
+        _ptr(scratch), _ptr(sinks), cross, 1 if out.dtype == torch.float32 else 0, _stream()))
 
 
 # Where the blocks that share a long row of logits meet (a 64-bit slot and a counter per row), per device.

@@ -65,6 +65,10 @@ class AttentionMixer(Mixer):
         self.v_head_dim = head_dim if v_head_dim is None else int(v_head_dim)
         self.sinks: Optional[torch.Tensor] = None
         self.values_in_keys = False
+        # Crossed values (set to the number of kv heads by mixers that combine heads' weights after the softmax): the
+        # kernels apply every query head's weights to the values of EVERY kv head, out is [T, heads, cross, v_head_dim].
+        # out may be float32 under bfloat16 inputs.
+        self.value_cross = 1
         self.weight_suffix = weight_suffix
         self.window = window
         self.chunk = int(chunk) if chunk else None
@@ -211,7 +215,7 @@ class AttentionMixer(Mixer):
     def tile_height(self) -> int:
         group = self.num_heads // self.num_kv_heads
         for bq in (16, 8, 4, 2, 1):
-            need = ops.attention_smem_bytes(bq, group, self.head_dim, self.v_head_dim)
+            need = ops.attention_smem_bytes(bq, group, self.head_dim, self.v_head_dim * self.value_cross)
             if need <= _SMEM_BUDGET or (bq == 1 and need <= _SMEM_LIMIT):
                 return bq
         raise ops.KernelError(
@@ -224,7 +228,8 @@ class AttentionMixer(Mixer):
         window = self.kernel_window()
         # the tensor-core kernels take values as wide as the keys (sinks and values in the key rows included)
         plain = self.v_head_dim == self.head_dim
-        key = ("attention_plan", self.num_heads, self.num_kv_heads, self.head_dim, window, dtype, plain)
+        cross = self.value_cross
+        key = ("attention_plan", self.num_heads, self.num_kv_heads, self.head_dim, window, dtype, plain, cross)
         plan = ctx.memo.get(key)
         if plan is not None:
             return plan
@@ -233,14 +238,16 @@ class AttentionMixer(Mixer):
             S = ctx.num_spans
             bound = ctx.max_pages * ctx.page_size          # the same for every step of this shape
             span = bound if window == 0 else min(bound, abs(window))
-            want = max(1, -(-2 * L.num_sms(ctx.device) // (S * self.num_kv_heads)))       # blocks to fill the SMs twice
-            nsplit = max(1, min(want, -(-span // 128)))
             mma = bf16 and ops.paged_decode_mma_supports(self.num_heads, self.num_kv_heads, self.head_dim)
+            # blocks to fill the SMs twice (the tensor-core kernel runs a block per pair of kv heads when values cross)
+            want = max(1, -(-2 * L.num_sms(ctx.device) // (S * self.num_kv_heads * (cross if mma else 1))))
+            nsplit = max(1, min(want, -(-span // 128)))
             if mma and span <= CLUSTER_MERGE_MAX_KEYS:
                 # Pieces that one thread-block cluster merges inside the kernel, which saves the merge kernel's
                 # round trip: at most 8 (larger clusters start more slowly), and no more blocks than are resident
                 # at once.
-                resident = ops.decode_mma_resident(self.head_dim) * L.num_sms(ctx.device) // (S * self.num_kv_heads)
+                resident = (ops.decode_mma_resident(self.head_dim) * L.num_sms(ctx.device)
+                            // (S * self.num_kv_heads * cross))
                 nsplit = max(1, min(8, ops.decode_mma_cluster_splits(), resident, -(-span // 128)))
             plan = ("decode_mma" if mma else "decode_simt", ctx.tiles(1), nsplit)
         else:
@@ -272,13 +279,15 @@ class AttentionMixer(Mixer):
         items = None
         if tensor:
             blocks_per_sm = 2 if self.head_dim <= 64 else 1
-            items = ctx.attention_items(1, window, None, self.num_heads, blocks_per_sm * L.num_sms(ctx.device),
+            items = ctx.attention_items(1, window, None, self.num_heads * self.value_cross,
+                                        blocks_per_sm * L.num_sms(ctx.device),
                                         select=tuple(tensor))
         decode = None
         if single:
             bound = ctx.max_pages * ctx.page_size
             span = bound if window == 0 else min(bound, abs(window))
-            resident = ops.decode_mma_resident(self.head_dim) * L.num_sms(ctx.device) // (len(single) * self.num_kv_heads)
+            resident = (ops.decode_mma_resident(self.head_dim) * L.num_sms(ctx.device)
+                        // (len(single) * self.num_kv_heads * self.value_cross))
             nsplit = max(1, min(8, ops.decode_mma_cluster_splits(), resident, -(-span // 128)))
             decode = (ctx.tiles(1, select=tuple(single)), nsplit)
         simt = []
@@ -299,7 +308,7 @@ class AttentionMixer(Mixer):
             if pos_key is None:
                 return None
         return ("attention", self.num_heads, self.num_kv_heads, self.head_dim, self.v_head_dim, self.kernel_window(),
-                self.sinks is not None, self.values_in_keys, pos_key)
+                self.sinks is not None, self.values_in_keys, self.value_cross, pos_key)
 
     def prepare(self, ctx, cache=None) -> None:
         self._plan(ctx, ctx.dtype)
@@ -320,11 +329,13 @@ class AttentionMixer(Mixer):
             (tile_span, tile_q0, ntiles), nsplit = plan[1], plan[2]
             scratch = None
             if nsplit > ops.decode_mma_cluster_splits():
-                scratch = torch.empty(ops.attention_scratch_floats(ntiles, self.num_heads, self.head_dim, 1, nsplit),
+                scratch = torch.empty(ops.attention_scratch_floats(ntiles, self.num_heads * self.value_cross,
+                                                                   self.head_dim, 1, nsplit),
                                       dtype=torch.float32, device=q.device)
             ops.paged_decode_mma(q, cache.k, v_plane, out, tile_span, tile_q0, ntiles, ctx.span_row, ctx.span_pos,
                                  ctx.block_tables[g], ctx.max_pages, ctx.page_size, self.num_heads,
-                                 self.num_kv_heads, self.head_dim, window, self.scale, nsplit, scratch, sinks=self.sinks)
+                                 self.num_kv_heads, self.head_dim, window, self.scale, nsplit, scratch, sinks=self.sinks,
+                                 cross=self.value_cross)
         elif plan[0] == "decode_simt":
             self._simt(q, cache, out, plan[1], common, 1, plan[2])
         else:
@@ -332,23 +343,26 @@ class AttentionMixer(Mixer):
             if items is not None:
                 tile_span, tile_q0, ntiles, cut = items
                 ops.paged_attention_tcgen05(q, cache.k, v_plane, out, tile_span, tile_q0, ntiles, *common, cut=cut,
-                                            sinks=self.sinks)
+                                            sinks=self.sinks, cross=self.value_cross)
             if decode is not None:
                 (tile_span, tile_q0, ntiles), nsplit = decode
                 ops.paged_decode_mma(q, cache.k, v_plane, out, tile_span, tile_q0, ntiles, ctx.span_row, ctx.span_pos,
                                      ctx.block_tables[g], ctx.max_pages, ctx.page_size, self.num_heads,
-                                     self.num_kv_heads, self.head_dim, window, self.scale, nsplit, None, sinks=self.sinks)
+                                     self.num_kv_heads, self.head_dim, window, self.scale, nsplit, None, sinks=self.sinks,
+                                     cross=self.value_cross)
             for tiles, bq, nsplit in simt:
                 self._simt(q, cache, out, tiles, common, bq, nsplit)
 
     def _simt(self, q, cache, out, tiles, common, bq, nsplit) -> None:
         tile_span, tile_q0, ntiles = tiles
         scratch = None
+        hdv = self.v_head_dim * self.value_cross           # crossed: a slot's whole value row, read by every head
         if nsplit > 1:
-            scratch = torch.empty(ops.attention_scratch_floats(ntiles, self.num_heads, self.v_head_dim, bq, nsplit),
+            scratch = torch.empty(ops.attention_scratch_floats(ntiles, self.num_heads, hdv, bq, nsplit),
                                   dtype=torch.float32, device=q.device)
         ops.paged_attention_simt(q, cache.k, cache.k if self.values_in_keys else cache.v, out, tile_span, tile_q0, ntiles,
-                                 *common, bq, nsplit, scratch, v_head_dim=self.v_head_dim, sinks=self.sinks)
+                                 *common, bq, nsplit, scratch, v_head_dim=hdv, sinks=self.sinks,
+                                 v_shared=self.value_cross > 1)
 
 
 register_part("mixer", "attention", AttentionMixer)

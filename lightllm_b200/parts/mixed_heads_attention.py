@@ -10,7 +10,6 @@ from ..config import register_part
 from ..csrc import ops
 from ..weights import WeightSpec
 from . import linear as L
-from .attention import FEW_ROWS, MANY_KEYS, _SMEM_BUDGET, _SMEM_LIMIT
 from .base import CacheView, LazyNorm
 from .conv_attention import ConvAttentionMixer, span_arrays
 
@@ -28,9 +27,11 @@ class MixedHeadsAttention(ConvAttentionMixer):
     * the concatenated heads are multiplied by ``sigmoid(W_g x)`` (``gate``: the tensor's name, or ``None``) before
       the output projection.
 
-    The mixed weights never exist: ``sum_j w'_h(j) v(j) = sum_g talk[h, g] sum_j w_g(j) v(j)``, so the attention kernel
-    runs every query head over the value rows of ALL kv heads (a slot's value row read whole, ``v_shared``) and one
-    kernel combines the ``heads x kv_heads`` results and gates them.  One contraction makes q | k | v | gate.
+    The mixed weights never exist: ``sum_j w'_h(j) v(j) = sum_g talk[h, g] sum_j w_g(j) v(j)``, so the attention kernels
+    apply every query head's weights to the values of ALL kv heads (``value_cross``: the tensor-core kernels for
+    portions and for single tokens when keys and values are 64 or 128 wide in bfloat16, else the CUDA-core kernel
+    reading a slot's value row whole) and one kernel combines the ``heads x kv_heads`` results and gates them.  One
+    contraction makes q | k | v | gate.
     Scores, softmax, the head sums, convolution sums, temperature and norms are float32 in both precisions."""
 
     def __init__(self, prefix: str, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, v_head_dim: int,
@@ -47,7 +48,7 @@ class MixedHeadsAttention(ConvAttentionMixer):
         self.v_unit_rms, self.norm_eps = bool(v_unit_rms), float(norm_eps)
         self.talk_name = f"{prefix}.{talk}" if talk else None
         self.gate_name = f"{prefix}.{gate}" if gate else None
-        self.shared_width = num_kv_heads * self.v_head_dim          # a slot's whole value row
+        self.value_cross = num_kv_heads
         self.w_fused = self.talk = None
 
     def cache_spec(self) -> CacheSpec:
@@ -75,59 +76,6 @@ class MixedHeadsAttention(ConvAttentionMixer):
         self.w_qkv = None
         self.talk = tensors[self.talk_name].float().contiguous() if self.talk_name else None
 
-    # ---- the step's plan: the CUDA-core kernels (they take value rows of any width) -------------------------------------
-    @property
-    def prepare_key(self):
-        return ("mixed_heads_attention", self.num_heads, self.num_kv_heads, self.head_dim, self.v_head_dim)
-
-    def tile_height(self) -> int:
-        group = self.num_heads // self.num_kv_heads
-        for bq in (16, 8, 4, 2, 1):
-            need = ops.attention_smem_bytes(bq, group, self.head_dim, self.shared_width)
-            if need <= _SMEM_BUDGET or (bq == 1 and need <= _SMEM_LIMIT):
-                return bq
-        raise ops.KernelError(f"attention over value rows of {self.shared_width} does not fit in shared memory")
-
-    def _plan(self, ctx, dtype):
-        key = ("mixed_heads_plan", self.num_heads, self.num_kv_heads, self.head_dim, self.v_head_dim)
-        plan = ctx.memo.get(key)
-        if plan is not None:
-            return plan
-        if ctx.decode_only:
-            bound = ctx.max_pages * ctx.page_size          # the same for every step of this shape
-            want = max(1, -(-2 * L.num_sms(ctx.device) // (ctx.num_spans * self.num_kv_heads)))
-            plan = [(ctx.tiles(1), 1, max(1, min(want, -(-bound // 128))))]
-        else:
-            rows, rest, rows_keys = [], [], 0
-            for i, s in enumerate(ctx.spans):
-                keys = s.start + s.length
-                if s.length < FEW_ROWS and keys >= MANY_KEYS:
-                    rows.append(i)
-                    rows_keys = max(rows_keys, keys)
-                else:
-                    rest.append(i)
-            plan = []
-            if rows:         # few rows over many keys: row by row, each row's keys in pieces
-                plan.append((ctx.tiles(1, select=tuple(rows)), 1, max(2, min(16, -(-rows_keys // 256)))))
-            if rest:
-                bq = self.tile_height()
-                plan.append((ctx.tiles(bq, select=tuple(rest)), bq, 1))
-        ctx.memo[key] = plan
-        return plan
-
-    def attend_all_values(self, q, cache: CacheView, ctx, out) -> None:
-        """out [T, H, G * vdim] float32: every query head's softmax weights applied to the values of every kv head."""
-        g = cache.group
-        for (tile_span, tile_q0, ntiles), bq, nsplit in self._plan(ctx, q.dtype):
-            scratch = None
-            if nsplit > 1:
-                scratch = torch.empty(ops.attention_scratch_floats(ntiles, self.num_heads, self.shared_width, bq, nsplit),
-                                      dtype=torch.float32, device=q.device)
-            ops.paged_attention_simt(q, cache.k, cache.v, out, tile_span, tile_q0, ntiles, ctx.span_row, ctx.span_len,
-                                     ctx.span_pos, ctx.block_tables[g], ctx.max_pages, ctx.page_size, self.num_heads,
-                                     self.num_kv_heads, self.head_dim, 0, self.scale, bq, nsplit, scratch,
-                                     v_head_dim=self.shared_width, v_shared=True)
-
     def forward(self, x, residual, ctx, cache: CacheView) -> None:
         if isinstance(x, LazyNorm):
             x = x.materialize()
@@ -147,8 +95,9 @@ class MixedHeadsAttention(ConvAttentionMixer):
                          tail_off, ctx.slot_mapping[cache.group], fuse_tail=ctx.decode_only and self.conv_taps > 1)
         if self.conv_taps > 1 and not ctx.decode_only:
             ops.conv_tail_update(fused, 0, self.channels, self.conv_taps, spans, cache.state, tail_off)
+        # every query head over every kv head's values, float32: the heads are summed before anything is rounded
         every = torch.empty((T, H * G * vd), dtype=torch.float32, device=x.device)
-        self.attend_all_values(q, cache, ctx, every)
+        self.attend(q, cache, ctx, every)
         heads = torch.empty((T, H * vd), dtype=x.dtype, device=x.device)
         gate = fused[:, self.channels:] if self.gate_name else None
         ops.talk_mix(every, self.talk, gate, heads, H, G, vd)

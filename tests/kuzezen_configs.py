@@ -63,8 +63,18 @@ KUZ_D = {"architecture": "Kuzezen", "vocab": 79, "width": 50, "embedding": {"sca
     _layer(_left(3, 1, 10, 7, 0.3, conv=3), _right(5, 6, 9, 15.0), 33),
     _layer(_left(5, 5, 6, 9, 0.4, conv=2, q_temp=(0.3, 11)), _right(3, 7, 5, 15.0), 17),
 ]}
-CONFIGS = {"A": KUZ_A, "B": KUZ_B, "C": KUZ_C, "D": KUZ_D}
-PAGE_SIZE = {"A": 16, "B": 16, "C": 8, "D": 16}
+# E: attention whose keys and values are both 64 or both 128 wide, with two or three kv heads and with as many as heads:
+# in bfloat16 the tensor-core attention kernels apply every head's weights to every kv head's values.  A loop of one
+# layer, a layer without feed-forward, a layer without temperature.
+KUZ_E = {"architecture": "Kuzezen", "vocab": 211, "width": 192, "embedding": {"scale": 14.0}, "norm": {"eps": 1e-6},
+         "canon": {"taps": 3}, "residual_mult": 0.6, "logit_softcap": 25.0, "loop": {"start": 1, "stop": 2, "times": 2},
+         "layers": [
+    _layer(_left(4, 2, 64, 64, 0.125, conv=3, q_temp=(0.3, 50)), _right(3, 64, 64, 15.0), 128),
+    _layer(_left(6, 3, 128, 128, 0.09, conv=2, q_temp=(0.2, 64)), _right(2, 128, 32, 10.0), None),
+    _layer(_left(2, 2, 64, 64, 0.125, conv=4), _right(1, 64, 128, 15.0), 256),
+]}
+CONFIGS = {"A": KUZ_A, "B": KUZ_B, "C": KUZ_C, "D": KUZ_D, "E": KUZ_E}
+PAGE_SIZE = {"A": 16, "B": 16, "C": 8, "D": 16, "E": 16}
 
 
 def config(name):

@@ -211,6 +211,58 @@ def test_attention_over_the_values_of_every_kv_head(dtype, H, G, hd, vd):
               rel=None if dtype == "float32" else 1.5e-2)
 
 
+@pytest.mark.parametrize("H,G,hd", [(4, 2, 64), (6, 3, 128), (2, 1, 64), (8, 2, 128), (4, 4, 64)])
+def test_tensor_core_attention_over_the_values_of_every_kv_head(H, G, hd):
+    """The same on the tensor-core kernels (bfloat16, keys and values 64 or 128 wide): portions on the tcgen05 kernel, whole
+    key ranges and ranges cut into pieces that a second kernel merges; single tokens on the decode kernel, its pieces
+    merged in a cluster and through scratch.  The result is float32.  One key far back carries most of a row's weight."""
+    torch.manual_seed(H * hd + G)
+    page, n = 16, 700
+    k, v = torch.randn(n, G, hd).to(torch.bfloat16), torch.randn(n, G, hd).to(torch.bfloat16)
+    kc, bt = paged(k, 64, page, "bfloat16")
+    vc = _same_pages(v, bt, page, "bfloat16")
+    scale = 1.5 / hd ** 0.5
+
+    def plain(q, start):
+        rows = q.shape[0]
+        pos = torch.arange(start, start + rows)
+        want = torch.zeros(rows, H, G, hd, dtype=torch.float64)
+        for h in range(H):
+            s = (q[:, h].double() @ k[:start + rows, h // (H // G)].double().T) * scale
+            s = s.masked_fill(torch.arange(start + rows)[None, :] > pos[:, None], float("-inf"))
+            w = torch.softmax(s, -1)
+            for g in range(G):
+                want[:, h, g] = w @ v[:start + rows, g].double()
+        return want
+
+    from lightllm_b200.engine.batch import Span, StepContext
+    for start, rows, pieces in ((0, 300, None), (380, 320, 2), (690, 10, None), (250, 135, 1), (3, 2, None)):
+        q = torch.randn(rows, H, hd).to(torch.bfloat16)
+        q[-1, 0] = k[3, 0] * 4.0
+        out = torch.full((rows, H * G * hd), float("nan"), device=DEV)
+        ctx = StepContext()
+        ctx.spans, ctx.device = [Span("a", 0, start, rows, 0)], DEV
+        ctx.iota, ctx.zeros = i32([0]), i32([0])
+        ts, tq, nt, cut = ctx.attention_items(1, 0, pieces, H * G, 296)
+        ops.paged_attention_tcgen05(dev(q).view(rows, H * hd), kc, vc, out, ts, tq, nt, i32([0]), i32([rows]), i32([start]),
+                                    bt, bt.shape[1], page, H, G, hd, 0, scale, cut=cut, cross=G)
+        ops.check_async_errors(DEV)
+        close(out.view(rows, H, G, hd), plain(q, start), "bfloat16", f"tcgen05, start {start}, {rows} rows, pieces of {pieces}",
+              rel=1.5e-2)
+    for pos in (n - 1, 130, 0):
+        for nsplit in (1, 4, 20):
+            q = torch.randn(1, H, hd).to(torch.bfloat16)
+            if pos > 3:
+                q[0, H - 1] = k[3, G - 1] * 4.0
+            out = torch.full((1, H * G * hd), float("nan"), device=DEV)
+            scratch = None
+            if nsplit > ops.decode_mma_cluster_splits():
+                scratch = torch.empty(ops.attention_scratch_floats(1, H * G, hd, 1, nsplit), device=DEV)
+            ops.paged_decode_mma(dev(q).view(1, H * hd), kc, vc, out, i32([0]), i32([0]), 1, i32([0]), i32([pos]), bt,
+                                 bt.shape[1], page, H, G, hd, 0, scale, nsplit, scratch, cross=G)
+            close(out.view(1, H, G, hd), plain(q, pos), "bfloat16", f"decode at {pos}, {nsplit} pieces", rel=1.5e-2)
+
+
 def _same_pages(v, bt, page, dtype):
     """The values laid into the pages that the block table ``bt`` names (the keys' pages)."""
     n = v.shape[0]
@@ -379,7 +431,7 @@ def variant_config(name, sharp=1.0):
 # The replay's weights.  C has no embedding scale and heads of 8 channels; with seed 3 one prompt position of it has a
 # memory head whose q . k nearly cancels under the unit norm's eps, and the plain implementation itself differs by
 # 3e-4 there between float32 and float64.  Seed 13 has no such position.
-REPLAY_SEED = {"A": 3, "B": 3, "C": 13, "D": 3}
+REPLAY_SEED = {"A": 3, "B": 3, "C": 13, "D": 3, "E": 3}
 
 
 def make_model(tmp_path, name, dtype, seed=3, sharp=1.0, edit=None):
@@ -420,7 +472,7 @@ def error(got, plain, dtype) -> float:
 
 
 LENGTHS = {"A": [1, 2, 17, 33, 70, 150, 64, 49], "B": [3, 40, 131, 330, 129, 520, 64, 257], "C": [1, 5, 40, 90, 33, 64, 17, 200],
-           "D": [1, 3, 20, 45, 16, 70, 33, 9]}
+           "D": [1, 3, 20, 45, 16, 70, 33, 9], "E": [2, 50, 140, 300, 127, 410, 64, 258]}
 
 
 def build_trace(name, cfg, seed=11):
@@ -437,7 +489,7 @@ def build_trace(name, cfg, seed=11):
         if len(seqs[rid]) > 1:
             tr.portions(f"p{rid}", [[16, 7, 2, 5, 3, 2], [2, 2, 9, 31, 4], [13, 2, 64, 3], [200, 33, 2, 129]][i % 4])
     prompt_len = {f"m{rid}": max(2, len(toks) - 12) if len(toks) > 14 else len(toks) for rid, toks in seqs.items()}
-    tr.mixed([f"m{rid}" for rid in seqs], prompt_len, seed=5, sizes=(2, 3, 7, 16, 40, 130) if name == "B" else (2, 3, 5, 7, 16))
+    tr.mixed([f"m{rid}" for rid in seqs], prompt_len, seed=5, sizes=(2, 3, 7, 16, 40, 130) if name in "BE" else (2, 3, 5, 7, 16))
     return tr, seqs
 
 
@@ -477,7 +529,7 @@ def only_attention(cfg, w):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "D", "E"])
 def test_sharp_attention_sees_far_keys_and_page_borders(tmp_path, name, dtype):
     """The attention's scale multiplied by 6 and every other path into the stream silenced, so that single keys carry a
     row's output: a key that is lost (far back, at a page's border, the first of the sequence) moves the logits by far more
@@ -485,11 +537,11 @@ def test_sharp_attention_sees_far_keys_and_page_borders(tmp_path, name, dtype):
     temperature steps pass under decoded tokens."""
     d, cfg, w = make_model(tmp_path, name, dtype, seed=8, sharp=6.0, edit=only_attention)
     rng = random.Random(2)
-    n = 420 if name == "B" else 200
+    n = {"B": 420, "E": 300}.get(name, 200)
     toks = [rng.randrange(cfg["vocab"]) for _ in range(n)]
     plain = plain_logits(toks, w, cfg)
     core = core_for(d, dtype, name)
-    got = stepwise(core, "a", toks, [129, 2, 150 - 131, 31, 2, 64] if name == "B" else [9, 2, 16, 38, 2, 70])
+    got = stepwise(core, "a", toks, [129, 2, 150 - 131, 31, 2, 64] if name in "BE" else [9, 2, 16, 38, 2, 70])
     err = error(got, plain, dtype)
     record(f"sharp Kuzezen {name} {dtype}", err, logits_std(plain))
     assert err <= atol_for(name + " sharp", dtype, plain)
@@ -531,7 +583,7 @@ def test_a_lost_state_shows(tmp_path, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "C", "D", "E"])
 def test_prefill_equals_token_by_token_and_long_decoding(tmp_path, name, dtype):
     """A whole prompt in one step against the same tokens one by one from the first (300 single steps: the memory, its
     running maximum and every convolution's tail are carried through every one)."""
@@ -549,7 +601,7 @@ def test_prefill_equals_token_by_token_and_long_decoding(tmp_path, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "D", "E"])
 def test_a_batch_of_unequal_requests_equals_each_alone_and_slots_are_used_again(tmp_path, name, dtype):
     d, cfg, w = make_model(tmp_path, name, dtype, seed=6)
     rng = random.Random(7)
