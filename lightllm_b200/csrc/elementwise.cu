@@ -119,10 +119,12 @@ LLB_EXPORT int llb_rmsnorm_add(const float* x, const void* w, int w_dtype, float
                                float scale, cudaStream_t stream) {
     if (T == 0) return 0;
     LLB_REQUIRE(T > 0 && D > 0 && x && w && dst, "rmsnorm_add: bad arguments");
-    const unsigned blocks = (unsigned)((T + 7) / 8);
-    if (w_dtype == LLB_F32) rmsnorm_add_kernel<float><<<blocks, 256, 0, stream>>>(x, (const float*)w, dst, T, D, eps, scale);
+    // a warp a row; few rows get a block of one warp each, so that they spread over the SMs
+    const int threads = T >= 2048 ? 256 : 32;
+    const unsigned blocks = (unsigned)((T + threads / 32 - 1) / (threads / 32));
+    if (w_dtype == LLB_F32) rmsnorm_add_kernel<float><<<blocks, threads, 0, stream>>>(x, (const float*)w, dst, T, D, eps, scale);
     else if (w_dtype == LLB_BF16)
-        rmsnorm_add_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(x, (const __nv_bfloat16*)w, dst, T, D, eps, scale);
+        rmsnorm_add_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(x, (const __nv_bfloat16*)w, dst, T, D, eps, scale);
     else return llb_fail("rmsnorm_add: unknown weight dtype %d", w_dtype);
     return llb_check_launch("rmsnorm_add");
 }

@@ -137,6 +137,55 @@ __global__ void __launch_bounds__(256) talk_mix_kernel(const TO_* __restrict__ o
         out[((size_t)t * H + h) * vd + d] = llb_from_float<TG>(a);
     }
 }
+
+// The same with a block per token: the token's H * G * vd results and the mixing matrix are read once, side by side,
+// into shared memory (float), and every thread sums its outputs from there.
+template <typename TO_, typename TG>
+__global__ void __launch_bounds__(256) talk_mix_staged_kernel(const TO_* __restrict__ o, const float* __restrict__ talk,
+                                                              const TG* __restrict__ gate, long long gate_stride,
+                                                              TG* __restrict__ out, int H, int G, int vd, int gated) {
+    extern __shared__ float tm_smem[];
+    const int n = H * G * vd;
+    float* so = tm_smem;          // [H, G, vd]
+    float* sw = tm_smem + n;      // [H, H]
+    const int t = blockIdx.x;
+    const TO_* row = o + (size_t)t * n;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) so[i] = llb_to_float(row[i]);
+    if (talk)
+        for (int i = threadIdx.x; i < H * H; i += blockDim.x) sw[i] = talk[i];
+    __syncthreads();
+    const TG* gr = gate + (size_t)t * gate_stride;
+    const int per = H / G;
+    for (int i = threadIdx.x; i < H * vd; i += blockDim.x) {
+        const int h = i / vd, d = i - h * vd;
+        const int c = h / per;
+        float a = 0.0f;
+        if (talk) {
+            const float* w = sw + h * H;
+            const float* col = so + c * vd + d;
+            for (int g = 0; g < H; ++g) a = fmaf(w[g], col[(size_t)g * G * vd], a);
+        } else {
+            a = so[((size_t)h * G + c) * vd + d];
+        }
+        if (gated) a *= 1.0f / (1.0f + expf(-llb_to_float(gr[i])));
+        out[(size_t)t * H * vd + i] = llb_from_float<TG>(a);
+    }
+}
+
+template <typename TO_, typename TG>
+int launch_talk_mix(const void* o, const float* talk, const void* gate, long long gate_stride, void* out, int T, int H, int G,
+                    int vd, int gated, cudaStream_t stream) {
+    const size_t smem = ((size_t)H * G * vd + (size_t)H * H) * sizeof(float);
+    if (smem <= 48 * 1024) {
+        talk_mix_staged_kernel<TO_, TG><<<(unsigned)T, 256, smem, stream>>>((const TO_*)o, talk, (const TG*)gate, gate_stride,
+                                                                            (TG*)out, H, G, vd, gated);
+        return llb_check_launch("talk_mix_staged");
+    }
+    const long long items = (long long)T * H;
+    talk_mix_kernel<TO_, TG><<<(unsigned)((items + 7) / 8), 256, 0, stream>>>((const TO_*)o, talk, (const TG*)gate, gate_stride,
+                                                                             (TG*)out, T, H, G, vd, gated);
+    return llb_check_launch("talk_mix");
+}
 }  // namespace
 
 // o [T, H, G, vd] (float, or the activation dtype); talk float [H, H] or null (no mixing: out_h = o[h, kv(h)]);
@@ -146,16 +195,13 @@ LLB_EXPORT int llb_talk_mix(const void* o, int o_dtype, const float* talk, const
                             void* out, int dtype, int T, int H, int G, int vd, cudaStream_t stream) {
     if (T == 0) return 0;
     LLB_REQUIRE(T > 0 && H > 0 && G > 0 && H % G == 0 && vd > 0 && o && out, "talk_mix: bad arguments");
-    const long long items = (long long)T * H;
-    const unsigned blocks = (unsigned)((items + 7) / 8);
     const int gated = gate != nullptr;
     if (!gated) gate = out;
     if (o_dtype == LLB_F32 && dtype == LLB_F32)
-        talk_mix_kernel<float, float><<<blocks, 256, 0, stream>>>((const float*)o, talk, (const float*)gate, gate_stride, (float*)out, T, H, G, vd, gated);
+        return launch_talk_mix<float, float>(o, talk, gate, gate_stride, out, T, H, G, vd, gated, stream);
     else if (o_dtype == LLB_F32 && dtype == LLB_BF16)
-        talk_mix_kernel<float, __nv_bfloat16><<<blocks, 256, 0, stream>>>((const float*)o, talk, (const __nv_bfloat16*)gate, gate_stride, (__nv_bfloat16*)out, T, H, G, vd, gated);
+        return launch_talk_mix<float, __nv_bfloat16>(o, talk, gate, gate_stride, out, T, H, G, vd, gated, stream);
     else if (o_dtype == LLB_BF16 && dtype == LLB_BF16)
-        talk_mix_kernel<__nv_bfloat16, __nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)o, talk, (const __nv_bfloat16*)gate, gate_stride, (__nv_bfloat16*)out, T, H, G, vd, gated);
-    else return llb_fail("talk_mix: unsupported dtypes %d, %d", o_dtype, dtype);
-    return llb_check_launch("talk_mix");
+        return launch_talk_mix<__nv_bfloat16, __nv_bfloat16>(o, talk, gate, gate_stride, out, T, H, G, vd, gated, stream);
+    return llb_fail("talk_mix: unsupported dtypes %d, %d", o_dtype, dtype);
 }

@@ -46,18 +46,22 @@ struct GateParams {
 
 __device__ __forceinline__ float log_sigmoid(float x) { return fminf(x, 0.0f) - log1pf(expf(-fabsf(x))); }
 
-// One warp per (span, head).
-__global__ void __launch_bounds__(128) memory_gates_kernel(GateParams p, int num_spans) {
-    const int lane = threadIdx.x & 31;
-    const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+// WARPS warps per (span, head): WARPS * 32 tokens a round.  A token's step is the map m -> max(lf + m, li); the composition
+// of steps is again of that form, (a, b): m -> max(a + m, b), so a warp scans its 32 steps with shuffles, the warps'
+// totals meet in shared memory, and every thread folds the totals of the warps before its own onto the running maximum.
+template <int WARPS>
+__global__ void __launch_bounds__(WARPS * 32) memory_gates_kernel(GateParams p, int num_spans) {
+    __shared__ float wa[WARPS], wb[WARPS];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const long long item = blockIdx.x;
     if (item >= (long long)num_spans * p.H) return;
     const int span = (int)(item / p.H), h = (int)(item - (long long)span * p.H);
     const int len = p.span_len[span], row0 = p.span_row[span];
     float* slot_m = p.state + (long long)p.span_slot[span] * p.state_stride + p.m_off + h;
     float m = p.span_pos[span] > 0 ? *slot_m : 0.0f;
     const float bi = p.bias_i ? p.bias_i[h] : 0.0f, bf = p.bias_f ? p.bias_f[h] : 0.0f;
-    for (int t0 = 0; t0 < len; t0 += 32) {
-        const int t = t0 + lane;
+    for (int t0 = 0; t0 < len; t0 += WARPS * 32) {
+        const int t = t0 + warp * 32 + lane;
         const bool valid = t < len;
         float li = -INFINITY, lf = 0.0f;          // the identity step for lanes past the end
         if (valid) {
@@ -74,18 +78,34 @@ __global__ void __launch_bounds__(128) memory_gates_kernel(GateParams p, int num
                 a = ea + a;
             }
         }
-        const float mt = fmaxf(a + m, b);
+        float m_in = m;                // the maximum before this warp's first token, and after the round's last
+        if (WARPS > 1) {
+            if (lane == 31) {
+                wa[warp] = a;
+                wb[warp] = b;
+            }
+            __syncthreads();
+            float run = m;
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) {
+                if (w == warp) m_in = run;
+                run = fmaxf(wa[w] + run, wb[w]);
+            }
+            m = run;
+            __syncthreads();           // the totals are read before the next round writes them
+        }
+        const float mt = fmaxf(a + m_in, b);
         float mp = __shfl_up_sync(0xffffffffu, mt, 1);
-        if (lane == 0) mp = m;
+        if (lane == 0) mp = m_in;
         if (valid) {
             const size_t at = (size_t)(row0 + t) * p.H + h;
             p.keep[at] = expf(lf + mp - mt);
             p.take[at] = expf(li - mt);
             p.floor_[at] = expf(-mt);
         }
-        m = __shfl_sync(0xffffffffu, mt, min(31, len - t0 - 1));
+        if (WARPS == 1) m = __shfl_sync(0xffffffffu, mt, 31);      // (lanes past the end are identity steps)
     }
-    if (lane == 0) *slot_m = m;
+    if (threadIdx.x == 0) *slot_m = m;
 }
 
 struct MemParams {
@@ -286,12 +306,12 @@ int launch_memory(const MemParams& p, int num_items, cudaStream_t stream) {
 
 }  // namespace
 
-// pre float [T, pre_stride] holds the gates' pre-activations (z_i of head h in column i_off + h, z_f in f_off + h);
+// pre float [T, pre_stride] (T rows over all spans) holds the gates' pre-activations (z_i of head h in column i_off + h, z_f in f_off + h);
 // bias_i, bias_f float [H] or null are added first; cap: the gates' soft cap.  The spans as in every kernel of a step.
 // state: float base of the requests' state plane, `state_stride` floats a slot, a request's running maximum m [H] at
 // `m_off` inside its slot (read where a span continues a request, written at the span's end).
 // keep, take, floor float [T, H]: exp(f + m' - m), exp(i - m), exp(-m) for every token and head.
-LLB_EXPORT int llb_memory_gates(const float* pre, long long pre_stride, int i_off, int f_off, const float* bias_i,
+LLB_EXPORT int llb_memory_gates(const float* pre, long long T, long long pre_stride, int i_off, int f_off, const float* bias_i,
                                 const float* bias_f, float cap, const int* span_row, const int* span_len,
                                 const int* span_pos, const int* span_slot, int num_spans, int H, float* state,
                                 long long state_stride, long long m_off, float* keep, float* take, float* floor_out,
@@ -305,7 +325,11 @@ LLB_EXPORT int llb_memory_gates(const float* pre, long long pre_stride, int i_of
     p.state = state; p.state_stride = state_stride; p.m_off = m_off; p.keep = keep; p.take = take; p.floor_ = floor_out;
     p.H = H;
     const long long items = (long long)num_spans * H;
-    memory_gates_kernel<<<(unsigned)((items + 3) / 4), 128, 0, stream>>>(p, num_spans);
+    LLB_REQUIRE(items < (1ll << 31), "memory_gates: too many spans and heads");
+    // rows per span on average: long spans take a block of eight warps each, single tokens a warp
+    if (T >= 128ll * num_spans) memory_gates_kernel<8><<<(unsigned)items, 256, 0, stream>>>(p, num_spans);
+    else if (T >= 48ll * num_spans) memory_gates_kernel<2><<<(unsigned)items, 64, 0, stream>>>(p, num_spans);
+    else memory_gates_kernel<1><<<(unsigned)items, 32, 0, stream>>>(p, num_spans);
     return llb_check_launch("memory_gates");
 }
 

@@ -403,7 +403,7 @@ def memory_gates(pre: torch.Tensor, i_off: int, f_off: int, bias_i: Optional[tor
         raise KernelError("memory_gates: pre must be contiguous float32 and hold both gates' columns")
     if m_off + H > stride or any(t.dtype != torch.float32 or t.numel() != T * H for t in (keep, take, floor)):
         raise KernelError("memory_gates: outputs must be float32 [T, H] and m must fit in a state slot")
-    _check(lib().llb_memory_gates(_ptr(pre), ctypes.c_longlong(C), i_off, f_off, _f32(bias_i, "bias_i"),
+    _check(lib().llb_memory_gates(_ptr(pre), ctypes.c_longlong(T), ctypes.c_longlong(C), i_off, f_off, _f32(bias_i, "bias_i"),
                                   _f32(bias_f, "bias_f"), ctypes.c_float(cap), _i32(span_row, "span_row"),
                                   _i32(span_len, "span_len"), _i32(span_pos, "span_pos"), _i32(span_slot, "span_slot"),
                                   num_spans, H, base, ctypes.c_longlong(stride), ctypes.c_longlong(m_off), _ptr(keep),

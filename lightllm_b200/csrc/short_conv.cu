@@ -134,11 +134,15 @@ __global__ void __launch_bounds__(128) conv_prepare_kernel(ConvParams p) {
             for (int e = 0; e < 2; ++e) {
                 if (d + e >= hd) continue;
                 const int c = cbase + d + e;
-                float keep[CONV_MAX_TAPS];
-                for (int j = 0; j + 1 < taps; ++j)          // positions pos - (taps - 2) + j: the old tail's j + 1, the token itself last
-                    keep[j] = j + 2 == taps ? llb_to_float(src[(size_t)t * p.row_stride + p.c0 + c])
-                                            : (pos - (taps - 2) + j >= 0 ? wtail[(size_t)(j + 1) * p.C + c] : 0.0f);
-                for (int j = 0; j + 1 < taps; ++j) wtail[(size_t)j * p.C + c] = keep[j];
+                float keep[CONV_MAX_TAPS];          // (loops of fixed length, so that it stays in registers)
+#pragma unroll
+                for (int j = 0; j + 1 < CONV_MAX_TAPS; ++j)          // positions pos - (taps - 2) + j: the old tail's j + 1, the token itself last
+                    if (j + 1 < taps)
+                        keep[j] = j + 2 == taps ? llb_to_float(src[(size_t)t * p.row_stride + p.c0 + c])
+                                                : (pos - (taps - 2) + j >= 0 ? wtail[(size_t)(j + 1) * p.C + c] : 0.0f);
+#pragma unroll
+                for (int j = 0; j + 1 < CONV_MAX_TAPS; ++j)
+                    if (j + 1 < taps) wtail[(size_t)j * p.C + c] = keep[j];
             }
         }
     }

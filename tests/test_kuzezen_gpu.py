@@ -122,6 +122,41 @@ def test_matrix_memory_kernels_over_spans_and_slots(dtype, H, d, e, chunk):
     assert torch.isfinite(state[2, off:off + mats + H]).all() and torch.isnan(state[1]).all()
 
 
+@pytest.mark.parametrize("lens", [(700, 300), (100, 60), (257, 31, 256), (5, 1, 33)])
+def test_memory_gates_of_long_spans(lens):
+    """The running maximum over spans long enough that several warps share a span's scan: spans that end inside a round
+    of the scan, at its edge and one past it; a span that continues from the maximum an earlier launch left; an input
+    gate at its cap for a stretch and a token that forgets."""
+    torch.manual_seed(sum(lens))
+    H, cap = 3, 12.0
+    bi, bf = torch.randn(H), torch.randn(H) + 1.0
+    state = torch.full((len(lens), H + 4), float("nan"), device=DEV)
+    m = [torch.zeros(H, dtype=torch.float64) for _ in lens]
+    at = [0] * len(lens)
+    for launch in range(2):
+        pres = [torch.randn(n, 2 * H + 2) * 3 for n in lens]
+        pres[0][lens[0] // 3:lens[0] // 3 + 5, 1:1 + H] = 100.0
+        pres[0][lens[0] // 2, 1 + H:1 + 2 * H] = -100.0
+        parts = [(str(i), i, at[i], at[i] + n) for i, n in enumerate(lens)]
+        T = sum(lens)
+        gates = torch.empty(3, T, H, device=DEV)
+        ops.memory_gates(dev(torch.cat(pres)), 1, 1 + H, dev(bi), dev(bf), cap, spans_of(parts), H, state, 2, gates[0],
+                         gates[1], gates[2])
+        want = torch.empty(3, T, H, dtype=torch.float64)
+        row = 0
+        for i, pre in enumerate(pres):
+            li = P.capped(pre.double()[:, 1:1 + H] + bi.double(), cap)
+            lf = torch.nn.functional.logsigmoid(P.capped(pre.double()[:, 1 + H:1 + 2 * H] + bf.double(), cap))
+            for t in range(lens[i]):
+                new = torch.maximum(lf[t] + m[i], li[t])
+                want[0, row], want[1, row], want[2, row] = (lf[t] + m[i] - new).exp(), (li[t] - new).exp(), (-new).exp()
+                m[i], row = new, row + 1
+            at[i] += lens[i]
+        close(gates, want, "float32", f"gates of spans {lens}, launch {launch}", rel=2e-5)
+        close(state[:, 2:2 + H], torch.stack(m), "float32", "the maxima left in the slots", rel=2e-6)
+    assert torch.isnan(state[:, :2]).all() and torch.isnan(state[:, 2 + H:]).all()
+
+
 def test_matrix_memory_maximum_starts_at_zero():
     """With gates far below zero at the first tokens the running maximum stays at 0 (it does not start at minus
     infinity), so the first outputs are small; an implementation that starts it at minus infinity gives outputs of
@@ -149,7 +184,8 @@ def test_matrix_memory_maximum_starts_at_zero():
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H,G,e", [(4, 2, 20), (6, 2, 6), (3, 3, 12), (2, 1, 14), (1, 1, 16), (6, 3, 64), (8, 4, 64)])
+@pytest.mark.parametrize("H,G,e", [(4, 2, 20), (6, 2, 6), (3, 3, 12), (2, 1, 14), (1, 1, 16), (6, 3, 64), (8, 4, 64),
+                                   (16, 8, 128)])         # (the last: too much for a block's shared memory)
 def test_head_mixing_and_gate(dtype, H, G, e):
     torch.manual_seed(H + e)
     T = 13
