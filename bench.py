@@ -381,7 +381,7 @@ def kuzezen_config(base: dict, layers: int, ff: bool = True) -> dict:
     return {"architecture": "Kuzezen", "vocab": base["vocab_size"], "width": D, "embedding": {"scale": 16.0},
             "norm": {"eps": 1e-6}, "canon": {"taps": 4}, "residual_mult": 0.5, "logit_softcap": 30.0,
             "loop": {"start": 0, "stop": inner, "times": 2},
-            "layers": [{"type": "parallel", "mixer": mixer, "mlp": mlp} for _ in range(inner + layers - 2 * inner)]}
+            "layers": [{"type": "parallel", "mixer": mixer, "mlp": mlp} for _ in range(max(1, inner + layers - 2 * inner))]}
 
 
 def run_design(name: str, sizes: str, layers: int, steps: int, warmup: int, only=None) -> int:

@@ -22,7 +22,7 @@ class CausalInputConv(InputFilter):
     (``last_reader``) brings it up to date.
 
     The kernel is the one that convolves fused projections (csrc/short_conv.cu), with the channels cut into "heads" of
-    up to 256 for its warps and ``h_t +`` folded into the last tap's weight."""
+    up to 64 for its warps and ``h_t +`` folded into the last tap's weight."""
 
     graph_safe = True
 
@@ -31,8 +31,9 @@ class CausalInputConv(InputFilter):
             raise ValueError(f"a convolution has at least one tap, got {taps}")
         self.name = f"{prefix}.{weight_name}" if prefix and weight_name else (prefix or weight_name)
         self.channels, self.taps, self.residual = int(channels), int(taps), bool(residual)
-        # the widest divisor of the channels that a warp of the kernel takes
-        self.piece = next(d for d in range(min(256, self.channels), 0, -1) if self.channels % d == 0)
+        # the widest divisor of the channels up to 64, a pair of channels a lane: narrow pieces give a single token's
+        # convolution to many warps instead of a few long loops
+        self.piece = next(d for d in range(min(64, self.channels), 0, -1) if self.channels % d == 0)
         self.weight = None
 
     def state_floats(self) -> int:
