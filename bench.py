@@ -369,17 +369,17 @@ def kuzezen_config(base: dict, layers: int, ff: bool = True) -> dict:
     """A Kuzezen model with the width, feed-forward, head count, head size and vocabulary of a Qwen2 configuration, run as
     ``layers`` layer runs: the first ``(layers - 1) // 2`` layers twice in a row (the loop), the one or two after them
     once.  Every layer has both mixers, each with
-    the base's heads and head size (the attention with the base's kv heads, three taps and a temperature that steps every
-    256 positions), and four input taps; ``ff=False`` leaves the feed-forwards out."""
+    the base's heads and head size (the attention with the base's kv heads, four taps and a temperature that steps every
+    128 positions), and three input taps; ``ff=False`` leaves the feed-forwards out."""
     D, H, G = base["hidden_size"], base["num_attention_heads"], base["num_key_value_heads"]
     hd = base.get("head_dim", D // H)
     inner = max(1, (layers - 1) // 2)
-    mixer = {"left": {"heads": H, "kv_heads": G, "dim": hd, "vdim": hd, "conv": 3, "scale": hd ** -0.5,
-                      "q_temp": {"coef": 0.3, "every": 256}},
-             "right": {"heads": H, "dim": hd, "vdim": hd, "gate_cap": 15.0}}
+    mixer = {"left": {"heads": H, "kv_heads": G, "dim": hd, "vdim": hd, "conv": 4, "scale": hd ** -0.5,
+                      "q_temp": {"coef": 0.25, "every": 128}},
+             "right": {"heads": H, "dim": hd, "vdim": hd, "gate_cap": 12.0}}
     mlp = {"kind": "dense", "ff": base["intermediate_size"]} if ff else None
-    return {"architecture": "Kuzezen", "vocab": base["vocab_size"], "width": D, "embedding": {"scale": 16.0},
-            "norm": {"eps": 1e-6}, "canon": {"taps": 4}, "residual_mult": 0.5, "logit_softcap": 30.0,
+    return {"architecture": "Kuzezen", "vocab": base["vocab_size"], "width": D, "embedding": {"scale": 10.0},
+            "norm": {"eps": 1e-5}, "canon": {"taps": 3}, "residual_mult": 0.7, "logit_softcap": 50.0,
             "loop": {"start": 0, "stop": inner, "times": 2},
             "layers": [{"type": "parallel", "mixer": mixer, "mlp": mlp} for _ in range(max(1, inner + layers - 2 * inner))]}
 
