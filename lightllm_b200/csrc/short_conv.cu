@@ -95,20 +95,33 @@ __global__ void __launch_bounds__(128) conv_prepare_kernel(ConvParams p) {
         const int d = 2 * (lane + 32 * i);
         y[i][0] = y[i][1] = 0.0f;
         if (d >= hd) continue;
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-            if (d + e >= hd) continue;
-            const int c = cbase + d + e;
-            float acc = 0.0f;
-            for (int j = 0; j < taps; ++j) {
+        {
+            // the lane's pair of channels tap by tap: one decision and one row address a tap for both
+            const bool two = d + 1 < hd;
+            const int c = cbase + d;
+            const float* w0 = p.w + (size_t)c * taps;
+            const T* r = src + ((long long)t - (taps - 1)) * p.row_stride + p.c0 + c;       // row t - (taps - 1) + j
+            const float* rt = tail + (size_t)local * p.C + c;                               // tail row local + j
+            float acc0 = 0.0f, acc1 = 0.0f;
+            for (int j = 0; j < taps; ++j, r += p.row_stride, rt += p.C) {
                 const int m = local - (taps - 1) + j;          // index within the span of the input this tap reads
-                float u = 0.0f;
-                if (m >= 0) u = llb_to_float(src[(size_t)(t - (taps - 1) + j) * p.row_stride + p.c0 + c]);
-                else if (pos - (taps - 1) + j >= 0) u = tail[(size_t)((taps - 1) + m) * p.C + c];
-                acc = fmaf(p.w[(size_t)c * taps + j], u, acc);
+                float u0 = 0.0f, u1 = 0.0f;
+                if (m >= 0) {
+                    u0 = llb_to_float(r[0]);
+                    if (two) u1 = llb_to_float(r[1]);
+                } else if (pos - (taps - 1) + j >= 0) {
+                    u0 = rt[0];
+                    if (two) u1 = rt[1];
+                }
+                acc0 = fmaf(w0[j], u0, acc0);
+                if (two) acc1 = fmaf(w0[taps + j], u1, acc1);
             }
-            if (sg.act == 1) acc = llb_silu(acc);
-            y[i][e] = acc;
+            if (sg.act == 1) {
+                acc0 = llb_silu(acc0);
+                acc1 = llb_silu(acc1);          // (0 stays 0)
+            }
+            y[i][0] = acc0;
+            y[i][1] = acc1;
         }
         if (d < sg.rotary_dim) {          // rotary_dim is even, so the pair lies inside it
             const float angle = (float)pos * p.freq[d >> 1];
