@@ -43,6 +43,7 @@ struct AttnParams {
     int v_shared;         // the value rows belong to no kv head: every query reads the whole row of hdv values of a slot
     int out_f32;          // out is float whatever the dtype of q and the caches
     float scale;
+    float softcap;        // > 0: a score s becomes softcap * tanh(s / softcap) before the softmax; 0: scores as they are
     float* part_acc;  // [tiles, Hkv, nsplit, BQ*G, hdv]
     float* part_ml;   // [tiles, Hkv, nsplit, BQ*G, 2]
 };
@@ -143,6 +144,7 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_kernel(AttnParams
                 float dot = 0.0f;
                 for (int d = 0; d < hd; ++d) dot = fmaf(qv[d], kr[d], dot);
                 s = dot * p.scale;
+                if (p.softcap > 0.0f) s = p.softcap * tanhf(s / p.softcap);
             }
             const float m_old = Ms[v];
             const float m_new = fmaxf(m_old, llb_warp_max(s));
@@ -357,7 +359,11 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_decode_kernel(AttnParams p)
 #pragma unroll
         for (int g = 0; g < GMAX; ++g) {
             if (g < G) {
-                const float sc = valid ? dot[g] * p.scale : -INFINITY;
+                float sc = -INFINITY;
+                if (valid) {
+                    sc = dot[g] * p.scale;
+                    if (p.softcap > 0.0f) sc = p.softcap * tanhf(sc / p.softcap);
+                }
                 const float m_new = fmaxf(m[g], llb_warp_max(sc));      // finite: the tile has a valid key
                 const float pr = valid ? expf(sc - m_new) : 0.0f;
                 const float corr = (m[g] == -INFINITY) ? 0.0f : expf(m[g] - m_new);
@@ -553,12 +559,13 @@ LLB_EXPORT long long llb_attention_scratch_floats(int num_tiles, int Hq, int hd,
 // v_shared != 0: v_cache is [slots, hdv] and every query head reads the whole row (out [T, Hq, hdv]): the products of a
 // head's softmax weights with the values of ALL kv heads, for mixers that combine heads' weights after the softmax.
 // out_f32 != 0: out is float whatever `dtype` says.
-LLB_EXPORT int llb_paged_attention_shared(const void* q, const void* k_cache, const void* v_cache, void* out, int dtype,
+// softcap > 0: every score (after `scale`) becomes softcap * tanh(score / softcap); sinks are not capped.
+LLB_EXPORT int llb_paged_attention_capped(const void* q, const void* k_cache, const void* v_cache, void* out, int dtype,
                                           const int* tile_span, const int* tile_q0, int num_tiles, const int* span_row,
                                           const int* span_len, const int* span_pos, const int* block_table,
                                           int max_pages, int page_size, int Hq, int Hkv, int hd, int hdv,
-                                          const float* sinks, int window, float scale, int BQ, int nsplit, float* scratch,
-                                          int v_shared, int out_f32, cudaStream_t stream) {
+                                          const float* sinks, int window, float scale, float softcap, int BQ, int nsplit,
+                                          float* scratch, int v_shared, int out_f32, cudaStream_t stream) {
     if (num_tiles == 0) return 0;
     LLB_REQUIRE(num_tiles > 0 && Hq > 0 && Hkv > 0 && hd > 0 && hdv > 0 && page_size > 0 && max_pages > 0 && BQ > 0,
                 "attention: bad sizes");
@@ -572,6 +579,7 @@ LLB_EXPORT int llb_paged_attention_shared(const void* q, const void* k_cache, co
     p.span_row = span_row; p.span_len = span_len; p.span_pos = span_pos; p.block_table = block_table;
     p.max_pages = max_pages; p.page_size = page_size; p.Hq = Hq; p.Hkv = Hkv; p.hd = hd;
     p.window = window; p.BQ = BQ; p.nsplit = nsplit; p.scale = scale;
+    p.softcap = softcap > 0.0f ? softcap : 0.0f;
     p.hdv = hdv; p.sinks = sinks;
     p.v_shared = v_shared ? 1 : 0; p.out_f32 = out_f32 ? 1 : 0;
     p.part_acc = scratch;
@@ -579,6 +587,17 @@ LLB_EXPORT int llb_paged_attention_shared(const void* q, const void* k_cache, co
     if (dtype == LLB_F32) return launch_attention<float>(p, num_tiles, stream);
     if (dtype == LLB_BF16) return launch_attention<__nv_bfloat16>(p, num_tiles, stream);
     return llb_fail("attention: unknown dtype %d", dtype);
+}
+
+LLB_EXPORT int llb_paged_attention_shared(const void* q, const void* k_cache, const void* v_cache, void* out, int dtype,
+                                          const int* tile_span, const int* tile_q0, int num_tiles, const int* span_row,
+                                          const int* span_len, const int* span_pos, const int* block_table,
+                                          int max_pages, int page_size, int Hq, int Hkv, int hd, int hdv,
+                                          const float* sinks, int window, float scale, int BQ, int nsplit, float* scratch,
+                                          int v_shared, int out_f32, cudaStream_t stream) {
+    return llb_paged_attention_capped(q, k_cache, v_cache, out, dtype, tile_span, tile_q0, num_tiles, span_row, span_len,
+                                      span_pos, block_table, max_pages, page_size, Hq, Hkv, hd, hdv, sinks, window, scale,
+                                      0.0f, BQ, nsplit, scratch, v_shared, out_f32, stream);
 }
 
 LLB_EXPORT int llb_paged_attention_ex(const void* q, const void* k_cache, const void* v_cache, void* out, int dtype,

@@ -205,3 +205,50 @@ LLB_EXPORT int llb_talk_mix(const void* o, int o_dtype, const float* talk, const
         return launch_talk_mix<__nv_bfloat16, __nv_bfloat16>(o, talk, gate, gate_stride, out, T, H, G, vd, gated, stream);
     return llb_fail("talk_mix: unsupported dtypes %d, %d", o_dtype, dtype);
 }
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Differential heads: a [T, H, M, vd] holds, for every head, the outputs of its M = 2 attention maps over the same values;
+// out[t, h, :] = unit_rms(a[t, h, 0, :] - lambda * a[t, h, 1, :]) * mult, the root mean square over the head's vd values
+// with eps inside the root and no weight.  One warp per (token, head), float arithmetic.
+namespace {
+
+template <typename TA, typename TO>
+__global__ void __launch_bounds__(256) diff_combine_kernel(const TA* __restrict__ a, TO* __restrict__ out, long long items, int vd,
+                                                           float lambda, float eps, float mult) {
+    const int lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= items) return;
+    const TA* a1 = a + (size_t)item * 2 * vd;
+    const TA* a2 = a1 + vd;
+    TO* o = out + (size_t)item * vd;
+    float ss = 0.0f;
+    for (int d = lane; d < vd; d += 32) {
+        const float v = llb_to_float(a1[d]) - lambda * llb_to_float(a2[d]);
+        ss += v * v;
+    }
+    const float inv = mult / sqrtf(llb_warp_sum(ss) / (float)vd + eps);
+    for (int d = lane; d < vd; d += 32)
+        o[d] = llb_from_float<TO>((llb_to_float(a1[d]) - lambda * llb_to_float(a2[d])) * inv);
+}
+
+}  // namespace
+
+// a [T, H, 2, vd] (float, or the dtype of out); out [T, H, vd] float or bf16.
+LLB_EXPORT int llb_diff_combine(const void* a, int a_dtype, void* out, int dtype, int T, int H, int vd, float lambda,
+                                float eps, float mult, cudaStream_t stream) {
+    if (T == 0) return 0;
+    LLB_REQUIRE(T > 0 && H > 0 && vd > 0 && a && out, "diff_combine: bad arguments");
+    const long long items = (long long)T * H;
+    const unsigned blocks = (unsigned)((items + 7) / 8);
+    if (a_dtype == LLB_F32 && dtype == LLB_F32)
+        diff_combine_kernel<float, float><<<blocks, 256, 0, stream>>>((const float*)a, (float*)out, items, vd, lambda, eps, mult);
+    else if (a_dtype == LLB_F32 && dtype == LLB_BF16)
+        diff_combine_kernel<float, __nv_bfloat16><<<blocks, 256, 0, stream>>>((const float*)a, (__nv_bfloat16*)out, items, vd,
+                                                                             lambda, eps, mult);
+    else if (a_dtype == LLB_BF16 && dtype == LLB_BF16)
+        diff_combine_kernel<__nv_bfloat16, __nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)a, (__nv_bfloat16*)out,
+                                                                                     items, vd, lambda, eps, mult);
+    else
+        return llb_fail("diff_combine: unsupported dtypes %d, %d", a_dtype, dtype);
+    return llb_check_launch("diff_combine");
+}

@@ -55,7 +55,7 @@ namespace {
 
 constexpr int F32 = 0, BF16 = 1;                 // the library's dtype codes
 constexpr int PAGE = 16;                         // tokens of a cache page
-constexpr int EXPECTED_ABI = 23;
+constexpr int EXPECTED_ABI = 24;
 constexpr int DECODE_ROWS = 64;                  // rows that the fused decode contractions take (their meeting place is sized for it)
 constexpr int CLUSTER_MERGE_MAX_KEYS = 8192;     // up to here the decode attention merges its pieces inside a cluster
 

@@ -2,6 +2,12 @@
 // `top` experts with the largest choice scores (score + an optional per-expert correction that takes part in the choice
 // only), weights = the chosen experts' scores (optionally renormalised to sum 1) times `scale`.
 //
+// Group-limited choice: the experts form `groups` equal groups of neighbours, a group's score is its largest choice
+// score, and only experts of the `keep` best groups can be chosen.  Identity experts: the router's outputs from `real` on
+// have no weights; a token's weights on them are summed into `idw` (the combine step adds idw * x), their entries of `ids`
+// are -1 (every later kernel skips such a pair) and `dense` has `real` columns.  Gate rows: the `n_gate` rows of w behind
+// the E routing rows give sigmoid(w . x) in `gate_out` (a per-token gate on a shared expert), from the same staged row.
+//
 // One block per token, a warp an expert's dot product.  The result is written twice: as lists (`ids`, `weights` [T, top], in the order of the choice) and
 // as a dense row of weights over all experts (`dense` [T, E], zero for the experts not chosen), which is what the
 // contraction-shaped expert path multiplies the experts' activations by.
@@ -15,7 +21,9 @@ template <typename TX>
 __global__ void __launch_bounds__(256) moe_route_kernel(const TX* __restrict__ x, const float* __restrict__ w,
                                                         const float* __restrict__ correction, int T, int D, int E, int top,
                                                         int softmax, int renorm, float scale, int* __restrict__ ids,
-                                                        float* __restrict__ weights, float* __restrict__ dense) {
+                                                        float* __restrict__ weights, float* __restrict__ dense, int real,
+                                                        int groups, int keep, float renorm_eps, int n_gate,
+                                                        float* __restrict__ idw, float* __restrict__ gate_out) {
     extern __shared__ __align__(16) float sm[];  // the token's row [D4], then score [E], choice [E]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
     const int t = blockIdx.x;
@@ -23,12 +31,13 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const TX* __restrict__ x
     float* xs = sm;
     float* score = sm + D4;
     float* choice = score + E;
+    float* gmax = choice + E;          // [groups]
     const TX* xr = x + (size_t)t * D;
     for (int d = threadIdx.x; d < D4; d += blockDim.x) xs[d] = d < D ? llb_to_float(xr[d]) : 0.0f;
     __syncthreads();
     // a warp an expert: the lanes' loads of a row are all in flight at once
     const bool vec = D % 4 == 0 && (uintptr_t)w % 16 == 0;
-    for (int e = warp; e < E; e += nwarps) {
+    for (int e = warp; e < E + n_gate; e += nwarps) {
         const float* wr = w + (size_t)e * D;
         float a0 = 0.0f, a1 = 0.0f;
         if (vec) {
@@ -43,7 +52,10 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const TX* __restrict__ x
             for (int d = lane; d < D; d += 32) a0 = fmaf(xs[d], wr[d], a0);
         }
         const float acc = llb_warp_sum(a0 + a1);
-        if (lane == 0) score[e] = acc;
+        if (lane == 0) {
+            if (e < E) score[e] = acc;
+            else gate_out[(size_t)t * n_gate + (e - E)] = 1.0f / (1.0f + expf(-acc));
+        }
     }
     __syncthreads();
     if (warp != 0) return;
@@ -61,9 +73,27 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const TX* __restrict__ x
     __syncwarp();
     for (int e = lane; e < E; e += 32) {
         choice[e] = score[e] + (correction ? correction[e] : 0.0f);
-        dense[(size_t)t * E + e] = 0.0f;
+        if (e < real) dense[(size_t)t * real + e] = 0.0f;
     }
     __syncwarp();
+    if (groups > 1 && keep < groups) {
+        // every lane walks the groups' maxima itself (a few dozen numbers): the `keep` best groups stay, lowest index first
+        // among equals; the others' choice scores become minus infinity
+        const int size = E / groups;
+        for (int g = lane; g < groups; g += 32) {
+            float m = -INFINITY;
+            for (int e = g * size; e < (g + 1) * size; ++e) m = fmaxf(m, choice[e]);
+            gmax[g] = m;
+        }
+        __syncwarp();
+        for (int g = lane; g < groups; g += 32) {
+            int better = 0;
+            for (int o = 0; o < groups; ++o) better += (gmax[o] > gmax[g] || (gmax[o] == gmax[g] && o < g)) ? 1 : 0;
+            if (better >= keep)
+                for (int e = g * size; e < (g + 1) * size; ++e) choice[e] = -INFINITY;
+        }
+        __syncwarp();
+    }
     float total = 0.0f;
     for (int k = 0; k < top; ++k) {
         float best = -INFINITY;
@@ -88,12 +118,23 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const TX* __restrict__ x
         }
         __syncwarp();
     }
-    const float mul = renorm ? scale / total : scale;
+    const float mul = renorm ? scale / (total + renorm_eps) : scale;
     __syncwarp();
+    float mine = 0.0f;
     for (int k = lane; k < top; k += 32) {
         const float wgt = weights[(size_t)t * top + k] * mul;
         weights[(size_t)t * top + k] = wgt;
-        dense[(size_t)t * E + ids[(size_t)t * top + k]] = wgt;
+        const int e = ids[(size_t)t * top + k];
+        if (e < real) {
+            dense[(size_t)t * real + e] = wgt;
+        } else {
+            mine += wgt;
+            ids[(size_t)t * top + k] = -1;
+        }
+    }
+    if (idw) {
+        mine = llb_warp_sum(mine);
+        if (lane == 0) idw[t] = mine;
     }
 }
 
@@ -121,7 +162,8 @@ __global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ 
     int* cursor = sh + E;
     for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
     __syncthreads();
-    for (int i = threadIdx.x; i < pairs; i += blockDim.x) atomicAdd(&count[ids[i]], 1);
+    for (int i = threadIdx.x; i < pairs; i += blockDim.x)
+        if (ids[i] >= 0) atomicAdd(&count[ids[i]], 1);          // a negative id: a pair without an expert (an identity)
     __syncthreads();
     if (threadIdx.x == 0) {
         int tile = 0;
@@ -133,7 +175,7 @@ __global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ 
         while (tile < max_tiles) tile_group[tile++] = 0;
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < pairs; i += blockDim.x) slot[i] = atomicAdd(&cursor[ids[i]], 1);
+    for (int i = threadIdx.x; i < pairs; i += blockDim.x) slot[i] = ids[i] >= 0 ? atomicAdd(&cursor[ids[i]], 1) : -1;
 }
 
 // xs[slot[i], :] = x[i / top, :]
@@ -141,6 +183,7 @@ template <typename TX>
 __global__ void __launch_bounds__(128) moe_gather_kernel(const TX* __restrict__ x, const int* __restrict__ slot, int top, int D,
                                                          TX* __restrict__ xs) {
     const int i = blockIdx.x;
+    if (slot[i] < 0) return;
     const TX* src = x + (size_t)(i / top) * D;
     TX* dst = xs + (size_t)slot[i] * D;
     constexpr int V = 16 / sizeof(TX);
@@ -152,14 +195,22 @@ __global__ void __launch_bounds__(128) moe_gather_kernel(const TX* __restrict__ 
     }
 }
 
-// residual[t, :] += sum_k weights[t, k] * y[slot[t * top + k], :], the choices added in their order
+// residual[t, :] += sum_k weights[t, k] * y[slot[t * top + k], :], the choices added in their order (a negative slot: a
+// pair without an expert, skipped), then + idw[t] * x[t, :] where identity experts were chosen (idw null: none).
+template <typename TX>
 __global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ slot,
                                                           const float* __restrict__ weights, int top, int D,
-                                                          float* __restrict__ residual) {
+                                                          float* __restrict__ residual, const TX* __restrict__ x,
+                                                          const float* __restrict__ idw) {
     const int t = blockIdx.x;
+    const float wi = idw ? idw[t] : 0.0f;
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
         float acc = 0.0f;
-        for (int k = 0; k < top; ++k) acc = fmaf(weights[(size_t)t * top + k], y[(size_t)slot[(size_t)t * top + k] * D + d], acc);
+        for (int k = 0; k < top; ++k) {
+            const int sl = slot[(size_t)t * top + k];
+            if (sl >= 0) acc = fmaf(weights[(size_t)t * top + k], y[(size_t)sl * D + d], acc);
+        }
+        if (idw) acc = fmaf(wi, llb_to_float(x[(size_t)t * D + d]), acc);
         residual[(size_t)t * D + d] += acc;
     }
 }
@@ -201,9 +252,10 @@ constexpr int PAIR_WARP_OUTS = PAIR_OUTS / 8;          // outputs a warp
 // act[pair, j] = silu(W_gate[e] x) * (W_up[e] x) with (gate_j, up_j) in rows 2j, 2j + 1 of expert e's block of w
 __global__ void __launch_bounds__(256) moe_pairs_gate_up_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                                                                 const int* __restrict__ ids, int top, int D, int F,
-                                                                __nv_bfloat16* __restrict__ act) {
+                                                                __nv_bfloat16* __restrict__ act, LlbGluArgs glu) {
     extern __shared__ __align__(16) float xs[];          // [D]
     const int pair = blockIdx.y, e = ids[pair];
+    if (e < 0) return;                                   // a pair without an expert
     const __nv_bfloat16* xr = x + (size_t)(pair / top) * D;
     for (int d = threadIdx.x; d < D; d += blockDim.x) xs[d] = __bfloat162float(xr[d]);
     __syncthreads();
@@ -215,12 +267,14 @@ __global__ void __launch_bounds__(256) moe_pairs_gate_up_kernel(const __nv_bfloa
         dot_rows_bf16<2 * PAIR_WARP_OUTS>(we + (size_t)(2 * j0) * D, xs, D, lane, acc);
         if (lane == 0)
             for (int i = 0; i < PAIR_WARP_OUTS; ++i)
-                act[(size_t)pair * F + j0 + i] = __float2bfloat16_rn(llb_silu(acc[2 * i]) * acc[2 * i + 1]);
+                act[(size_t)pair * F + j0 + i] =
+                    __float2bfloat16_rn(llb_glu(acc[2 * i], acc[2 * i + 1], glu.kind, glu.alpha, glu.limit, glu.up_shift));
     } else {
         for (int j = j0; j < F; ++j) {
             float acc[2];
             dot_rows_bf16<2>(we + (size_t)(2 * j) * D, xs, D, lane, acc);
-            if (lane == 0) act[(size_t)pair * F + j] = __float2bfloat16_rn(llb_silu(acc[0]) * acc[1]);
+            if (lane == 0)
+                act[(size_t)pair * F + j] = __float2bfloat16_rn(llb_glu(acc[0], acc[1], glu.kind, glu.alpha, glu.limit, glu.up_shift));
         }
     }
 }
@@ -230,6 +284,11 @@ __global__ void __launch_bounds__(256) moe_pairs_down_kernel(const __nv_bfloat16
                                                              const int* __restrict__ ids, int D, int F, float* __restrict__ y) {
     extern __shared__ __align__(16) float as[];          // [F]
     const int pair = blockIdx.y, e = ids[pair];
+    if (e < 0) {                                         // a pair without an expert: zeros, which the combine step skips anyway
+        for (int d = blockIdx.x * PAIR_OUTS + threadIdx.x; d < D && d < (blockIdx.x + 1) * PAIR_OUTS; d += blockDim.x)
+            y[(size_t)pair * D + d] = 0.0f;
+        return;
+    }
     for (int f = threadIdx.x; f < F; f += blockDim.x) as[f] = __bfloat162float(act[(size_t)pair * F + f]);
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -253,18 +312,26 @@ __global__ void __launch_bounds__(256) moe_pairs_down_kernel(const __nv_bfloat16
 
 // The experts of a few pairs, read pair by pair (bfloat16; D and F multiples of 8): x [T, D]; ids int [T * top]; w_gate_up
 // [E * 2F, D] with (gate_j, up_j) in neighbouring rows; w_down [E * D, F]; act [T * top, F] scratch; y float [T * top, D].
-LLB_EXPORT int llb_moe_pairs(const void* x, const int* ids, int pairs, int top, int D, int F, const void* w_gate_up,
-                             const void* w_down, void* act, float* y, cudaStream_t stream) {
+// The gated activation is llb_glu(kind, alpha, limit, up_shift); a pair whose id is negative has no expert (y = 0).
+LLB_EXPORT int llb_moe_pairs_glu(const void* x, const int* ids, int pairs, int top, int D, int F, const void* w_gate_up,
+                                 const void* w_down, void* act, float* y, int glu_kind, float glu_alpha, float glu_limit,
+                                 float glu_up_shift, cudaStream_t stream) {
     if (pairs == 0) return 0;
     LLB_REQUIRE(pairs > 0 && top > 0 && x && ids && w_gate_up && w_down && act && y, "moe_pairs: bad arguments");
     LLB_REQUIRE(D > 0 && F > 0 && D % 8 == 0 && F % 8 == 0 && D <= 12288 && F <= 12288, "moe_pairs: D=%d, F=%d must be multiples of 8", D, F);
     moe_pairs_gate_up_kernel<<<dim3((F + PAIR_OUTS - 1) / PAIR_OUTS, pairs), 256, D * sizeof(float), stream>>>(
-        (const __nv_bfloat16*)x, (const __nv_bfloat16*)w_gate_up, ids, top, D, F, (__nv_bfloat16*)act);
+        (const __nv_bfloat16*)x, (const __nv_bfloat16*)w_gate_up, ids, top, D, F, (__nv_bfloat16*)act,
+        LlbGluArgs{glu_kind, glu_alpha, glu_limit, glu_up_shift});
     int rc = llb_check_launch("moe_pairs_gate_up");
     if (rc) return rc;
     moe_pairs_down_kernel<<<dim3((D + PAIR_OUTS - 1) / PAIR_OUTS, pairs), 256, F * sizeof(float), stream>>>(
         (const __nv_bfloat16*)act, (const __nv_bfloat16*)w_down, ids, D, F, y);
     return llb_check_launch("moe_pairs_down");
+}
+
+LLB_EXPORT int llb_moe_pairs(const void* x, const int* ids, int pairs, int top, int D, int F, const void* w_gate_up,
+                             const void* w_down, void* act, float* y, cudaStream_t stream) {
+    return llb_moe_pairs_glu(x, ids, pairs, top, D, F, w_gate_up, w_down, act, y, LLB_GLU_SILU, 1.0f, 0.0f, 0.0f, stream);
 }
 
 // ids int [T * top] -> slot int [T * top], tile_group int [max_tiles] (see moe_sort_kernel); max_tiles >= T * top / align + E.
@@ -289,39 +356,71 @@ LLB_EXPORT int llb_moe_gather(const void* x, int dtype, const int* slot, int pai
     return llb_check_launch("moe_gather");
 }
 
-// y float [rows, D], slot int [T * top], weights float [T, top], residual float [T, D] += the weighted rows.
-LLB_EXPORT int llb_moe_combine(const float* y, const int* slot, const float* weights, int T, int top, int D, float* residual,
-                               cudaStream_t stream) {
+// y float [rows, D], slot int [T * top] (negative: skipped), weights float [T, top], residual float [T, D] += the weighted
+// rows, + idw[t] * x[t] (x [T, D] float or bf16, idw float [T]; both null: no identity experts).  top may be 0 (y, slot and
+// weights unused): the identity term alone.
+LLB_EXPORT int llb_moe_combine_identity(const float* y, const int* slot, const float* weights, int T, int top, int D,
+                                        float* residual, const void* x, int x_dtype, const float* idw, cudaStream_t stream) {
     if (T == 0) return 0;
-    LLB_REQUIRE(T > 0 && top > 0 && D > 0 && y && slot && weights && residual, "moe_combine: bad arguments");
-    moe_combine_kernel<<<T, 256, 0, stream>>>(y, slot, weights, top, D, residual);
+    LLB_REQUIRE(T > 0 && top >= 0 && D > 0 && residual && (top == 0 || (y && slot && weights)), "moe_combine: bad arguments");
+    LLB_REQUIRE((x == nullptr) == (idw == nullptr), "moe_combine: the identity term needs both x and its weights");
+    if (x_dtype == LLB_BF16 && x)
+        moe_combine_kernel<__nv_bfloat16><<<T, 256, 0, stream>>>(y, slot, weights, top, D, residual, (const __nv_bfloat16*)x, idw);
+    else if (x_dtype == LLB_F32 || !x)
+        moe_combine_kernel<float><<<T, 256, 0, stream>>>(y, slot, weights, top, D, residual, (const float*)x, idw);
+    else
+        return llb_fail("moe_combine: unknown dtype %d", x_dtype);
     return llb_check_launch("moe_combine");
 }
 
-// x [T, D] float or bf16; w float [E, D]; correction float [E] or null; ids int [T, top]; weights float [T, top];
-// dense float [T, E].  softmax != 0: scores by a softmax over the experts, else by a sigmoid of each logit;
-// renorm != 0: the chosen scores are divided by their sum before `scale`.
-LLB_EXPORT int llb_moe_route(const void* x, int x_dtype, const float* w, const float* correction, int T, int D, int E,
-                             int top, int softmax, int renorm, float scale, int* ids, float* weights, float* dense,
-                             cudaStream_t stream) {
+LLB_EXPORT int llb_moe_combine(const float* y, const int* slot, const float* weights, int T, int top, int D, float* residual,
+                               cudaStream_t stream) {
+    return llb_moe_combine_identity(y, slot, weights, T, top, D, residual, nullptr, LLB_F32, nullptr, stream);
+}
+
+// x [T, D] float or bf16; w float [E + n_gate, D]; correction float [E] or null; ids int [T, top]; weights float [T, top];
+// dense float [T, real].  softmax != 0: scores by a softmax over the E outputs, else by a sigmoid of each logit;
+// renorm != 0: the chosen scores are divided by their sum (+ renorm_eps) before `scale`.  real <= E: the outputs from
+// `real` on are identity experts (ids -1, their weights summed into idw float [T]).  groups > 1: only experts of the `keep`
+// best of `groups` equal groups of neighbours can be chosen.  n_gate > 0: gate_out float [T, n_gate] = sigmoid of the
+// rows of w behind the routing rows.
+LLB_EXPORT int llb_moe_route_ex(const void* x, int x_dtype, const float* w, const float* correction, int T, int D, int E,
+                                int real, int top, int softmax, int renorm, float renorm_eps, float scale, int groups,
+                                int keep, int n_gate, int* ids, float* weights, float* dense, float* idw, float* gate_out,
+                                cudaStream_t stream) {
     if (T == 0) return 0;
     LLB_REQUIRE(T > 0 && D > 0 && x && w && ids && weights && dense, "moe_route: bad arguments");
     LLB_REQUIRE(E > 0 && E <= MOE_MAX_EXPERTS && top > 0 && top <= E, "moe_route: top %d of %d experts (at most %d)", top, E,
                 MOE_MAX_EXPERTS);
-    // a block a token; as many warps as there are experts to walk side by side, at most eight
-    const int warps = E < 8 ? (E < 1 ? 1 : E) : 8;
-    const size_t smem = (size_t)(((D + 3) & ~3) + 2 * E) * sizeof(float);
+    LLB_REQUIRE(real >= 0 && real <= E && (real == E || idw != nullptr), "moe_route: %d of %d outputs have experts", real, E);
+    LLB_REQUIRE(groups >= 0 && (groups <= 1 || (E % groups == 0 && keep >= 1 && keep <= groups)),
+                "moe_route: %d experts in %d groups of which %d are kept", E, groups, keep);
+    LLB_REQUIRE(groups <= 1 || (long long)keep * (E / groups) >= top, "moe_route: the kept groups hold fewer than %d experts", top);
+    LLB_REQUIRE(n_gate >= 0 && (n_gate == 0 || gate_out != nullptr), "moe_route: gate rows without an output");
+    // a block a token; as many warps as there are rows to walk side by side, at most eight
+    const int rows = E + n_gate;
+    const int warps = rows < 8 ? rows : 8;
+    const size_t smem = (size_t)(((D + 3) & ~3) + 2 * E + (groups > 1 ? groups : 0)) * sizeof(float);
     LLB_REQUIRE(smem <= 48 * 1024, "moe_route: rows of %d numbers do not fit in shared memory", D);
     const unsigned blocks = (unsigned)T;
     if (x_dtype == LLB_F32)
         moe_route_kernel<float><<<blocks, warps * 32, smem, stream>>>((const float*)x, w, correction, T, D, E, top, softmax,
-                                                                      renorm, scale, ids, weights, dense);
+                                                                      renorm, scale, ids, weights, dense, real, groups, keep,
+                                                                      renorm_eps, n_gate, idw, gate_out);
     else if (x_dtype == LLB_BF16)
-        moe_route_kernel<__nv_bfloat16><<<blocks, warps * 32, smem, stream>>>((const __nv_bfloat16*)x, w, correction, T, D, E,
-                                                                              top, softmax, renorm, scale, ids, weights, dense);
+        moe_route_kernel<__nv_bfloat16><<<blocks, warps * 32, smem, stream>>>(
+            (const __nv_bfloat16*)x, w, correction, T, D, E, top, softmax, renorm, scale, ids, weights, dense, real, groups,
+            keep, renorm_eps, n_gate, idw, gate_out);
     else
         return llb_fail("moe_route: unknown dtype %d", x_dtype);
     return llb_check_launch("moe_route");
+}
+
+LLB_EXPORT int llb_moe_route(const void* x, int x_dtype, const float* w, const float* correction, int T, int D, int E,
+                             int top, int softmax, int renorm, float scale, int* ids, float* weights, float* dense,
+                             cudaStream_t stream) {
+    return llb_moe_route_ex(x, x_dtype, w, correction, T, D, E, E, top, softmax, renorm, 0.0f, scale, 0, 0, 0, ids, weights,
+                            dense, nullptr, nullptr, stream);
 }
 
 // act [T, E * F] (float or bf16), in place: the activations of expert e of row t times dense[t, e].

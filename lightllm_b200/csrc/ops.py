@@ -17,7 +17,7 @@ from . import build as _build
 
 F32, BF16 = 0, 1
 EPI_STORE, EPI_STORE_F32, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2, 3
-ABI_VERSION = 23
+ABI_VERSION = 24
 
 _lib: Optional[ctypes.CDLL] = None
 
@@ -246,13 +246,14 @@ def paged_attention_simt(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
                          num_heads: int, num_kv_heads: int, head_dim: int, window: int, scale: float,
                          bq: int, nsplit: int = 1, scratch: Optional[torch.Tensor] = None,
                          v_head_dim: Optional[int] = None, sinks: Optional[torch.Tensor] = None,
-                         v_shared: bool = False) -> None:
+                         v_shared: bool = False, softcap: float = 0.0) -> None:
     """Attention of every query row of the listed tiles over its request's pages.  ``v_head_dim``: width of a value
     row (and of an output row) when it differs from the keys'; ``v_cache`` may be ``k_cache`` itself (values read out
     of the key rows).  ``sinks`` float32 [num_heads]: ``exp(sinks[h])`` joins head h's softmax denominator once.
     ``v_shared``: a slot's value row (``v_head_dim`` wide: all kv heads side by side) is read whole by every query head,
     so ``out`` [T, num_heads, v_head_dim] holds each head's weights applied to the values of every kv head.  ``out`` may
-    be float32 under bfloat16 inputs."""
+    be float32 under bfloat16 inputs.  ``softcap`` > 0: a score becomes ``softcap * tanh(score / softcap)`` (sinks are
+    not capped)."""
     hdv = head_dim if v_head_dim is None else v_head_dim
     if k_cache.dtype != q.dtype or v_cache.dtype != q.dtype or out.dtype not in (q.dtype, torch.float32):
         raise KernelError("attention: q and the caches must share a dtype, out has it or is float32")
@@ -264,12 +265,12 @@ def paged_attention_simt(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
         need = attention_scratch_floats(num_tiles, num_heads, hdv, bq, nsplit)
         if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need:
             raise KernelError(f"attention: nsplit={nsplit} needs {need} floats of scratch")
-    _check(lib().llb_paged_attention_shared(
+    _check(lib().llb_paged_attention_capped(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _dt(q),
         _i32(tile_span, "tile_span"), _i32(tile_q0, "tile_q0"), num_tiles,
         _i32(span_row, "span_row"), _i32(span_len, "span_len"), _i32(span_pos, "span_pos"),
         _i32(block_table, "block_table"), max_pages, page_size, num_heads, num_kv_heads, head_dim, hdv, _ptr(sinks),
-        window, ctypes.c_float(scale), bq, nsplit, _ptr(scratch), 1 if v_shared else 0,
+        window, ctypes.c_float(scale), ctypes.c_float(softcap or 0.0), bq, nsplit, _ptr(scratch), 1 if v_shared else 0,
         1 if out.dtype == torch.float32 and q.dtype != torch.float32 else 0, _stream()))
 
 
@@ -479,6 +480,63 @@ def qkv_prepare(src: torch.Tensor, q_off: int, k_off: int, v_off: int, num_heads
                                  _ptr(v_cache), _stream()))
 
 
+def head_prepare(src: torch.Tensor, q_off: int, k_off: int, num_q_heads: int, num_k_heads: int, head_dim: int,
+                 positions: torch.Tensor, slot_mapping: Optional[torch.Tensor], q_out: Optional[torch.Tensor],
+                 k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], *, q_maps: int = 1,
+                 values: Optional[str] = None, v_off: int = -1, v_width: int = 0,
+                 q_norm_w: Optional[torch.Tensor] = None, k_norm_w: Optional[torch.Tensor] = None, eps: float = 0.0,
+                 inv_freq: Optional[torch.Tensor] = None, rotary_dim: int = 0, interleaved: bool = False) -> None:
+    """From a fused projection ``src`` [T, C] with ``num_q_heads`` query heads at ``q_off`` and ``num_k_heads`` key heads
+    at ``k_off`` (each ``head_dim`` wide): per head an optional RMS norm with a weight [head_dim] shared by the heads
+    (float32), then the rotation of the first ``rotary_dim`` dimensions; queries to ``q_out``, keys to the cache rows
+    ``slot_mapping`` names (``None``: nothing is cached).  ``q_maps`` = M > 1 writes query head i as a row of
+    ``M * head_dim`` numbers with the head at offset ``(i % M) * head_dim`` and zeros elsewhere (attention with M score
+    maps a head over key rows that hold a kv head's maps side by side).  ``values``: ``None`` no value rows, ``"columns"``
+    the ``v_width`` numbers at ``v_off`` are copied to the slot's value row, ``"keys"`` the value row is the key row as
+    projected (before norm and rotation)."""
+    T, C = src.shape
+    for off, n in ((q_off, num_q_heads * head_dim), (k_off, num_k_heads * head_dim), (v_off, v_width)):
+        if n and off >= 0 and off + n > C:
+            raise KernelError(f"head_prepare: columns {off}..{off + n} lie outside the {C} of src")
+    if src.stride(1) != 1:
+        raise KernelError("head_prepare: the rows of src must be dense")
+    if num_q_heads and (q_out is None or q_out.dtype != src.dtype or q_out.numel() != T * num_q_heads * q_maps * head_dim):
+        raise KernelError("head_prepare: q_out does not fit")
+    v_mode = {None: 0, "columns": 1, "keys": 2}[values]
+    if slot_mapping is not None and num_k_heads:
+        if k_cache is None or k_cache.dtype != src.dtype or k_cache[0].numel() != num_k_heads * head_dim:
+            raise KernelError("head_prepare: k_cache does not fit")
+        want = {0: None, 1: v_width, 2: num_k_heads * head_dim}[v_mode]
+        if want is not None and (v_cache is None or v_cache.dtype != src.dtype or v_cache[0].numel() != want):
+            raise KernelError("head_prepare: v_cache does not fit")
+    for w_ in (q_norm_w, k_norm_w):
+        if w_ is not None and (w_.dtype != torch.float32 or w_.numel() != head_dim):
+            raise KernelError("head_prepare: a norm weight is float32 [head_dim], shared by the heads")
+    if rotary_dim and (inv_freq is None or inv_freq.numel() != rotary_dim // 2):
+        raise KernelError("head_prepare: inv_freq must be float32 [rotary_dim/2]")
+    writes = slot_mapping is not None
+    _check(lib().llb_head_prepare(_ptr(src), _dt(src), ctypes.c_longlong(src.stride(0)), q_off, k_off, v_off, T, num_q_heads,
+                                  num_k_heads if writes else 0, head_dim, q_maps, v_mode if writes else 0, v_width,
+                                  _f32(q_norm_w, "q_norm_w"), _f32(k_norm_w, "k_norm_w"), ctypes.c_float(eps),
+                                  _i32(positions, "positions"), _f32(inv_freq, "inv_freq"), rotary_dim,
+                                  1 if interleaved else 0, _i32(slot_mapping, "slot_mapping"), _ptr(q_out),
+                                  _ptr(k_cache) if writes else None, _ptr(v_cache) if writes else None, _stream()))
+
+
+def diff_combine(a: torch.Tensor, out: torch.Tensor, num_heads: int, v_head_dim: int, lam: float, eps: float,
+                 mult: float) -> None:
+    """``a`` [T, heads, 2, v_head_dim] (float32 or the dtype of ``out``): the outputs of every head's two attention maps;
+    ``out[t, h] = unit_rms(a[t, h, 0] - lam * a[t, h, 1]) * mult`` with the root mean square over the head's values and
+    ``eps`` inside the root."""
+    T = out.shape[0]
+    if a.numel() != T * num_heads * 2 * v_head_dim or out.numel() != T * num_heads * v_head_dim:
+        raise KernelError("diff_combine: sizes do not fit")
+    if a.dtype not in (torch.float32, out.dtype):
+        raise KernelError("diff_combine: a is float32 or has the dtype of out")
+    _check(lib().llb_diff_combine(_ptr(a), _dt(a), _ptr(out), _dt(out), T, num_heads, v_head_dim, ctypes.c_float(lam),
+                                  ctypes.c_float(eps), ctypes.c_float(mult), _stream()))
+
+
 def head_linear(x: torch.Tensor, x_off: int, w: torch.Tensor, out: torch.Tensor) -> None:
     """out[t, h, :] = w[h] @ x[t, x_off + h*in : x_off + (h+1)*in] for w [H, out, in]; x [T, C], out [T, H*out]."""
     T, C = x.shape
@@ -660,18 +718,31 @@ def low_rank_up(x: torch.Tensor, x_off: int, w: torch.Tensor, out: torch.Tensor,
 
 def moe_route(x: torch.Tensor, w: torch.Tensor, correction: Optional[torch.Tensor], top: int, scale: float,
               ids: torch.Tensor, weights: torch.Tensor, dense: torch.Tensor, softmax: bool = False,
-              renormalize: bool = False) -> None:
-    """Routing in float (csrc/moe.cu): x [T, D], w float32 [E, D], correction float32 [E] or None (joins the choice, not
-    the weights); ids int32 [T, top], weights float32 [T, top], dense float32 [T, E] (zero where not chosen)."""
+              renormalize: bool = False, *, renorm_eps: float = 0.0, real: Optional[int] = None, groups: int = 0,
+              keep: int = 0, identity_weight: Optional[torch.Tensor] = None, gate_rows: int = 0,
+              gate_out: Optional[torch.Tensor] = None) -> None:
+    """Routing in float (csrc/moe.cu): x [T, D], w float32 [E + gate_rows, D], correction float32 [E] or None (joins the
+    choice, not the weights); ids int32 [T, top], weights float32 [T, top], dense float32 [T, real] (zero where not chosen).
+    ``real`` < E: the router's outputs from ``real`` on are identity experts; their entries of ``ids`` are -1 and a
+    token's weights on them are summed into ``identity_weight`` float32 [T].  ``groups`` > 1: only experts of the ``keep``
+    best of ``groups`` equal groups of neighbours can be chosen (a group's score is its largest choice score).
+    ``gate_rows``: that many further rows of w give ``gate_out`` float32 [T, gate_rows] = sigmoid(w . x)."""
     T, D = x.shape
-    E = w.shape[0]
+    E = w.shape[0] - gate_rows
+    real = E if real is None else real
     if w.dtype != torch.float32 or w.shape[1] != D or (correction is not None and correction.numel() != E):
         raise KernelError("moe_route: the router's weights must be float32 [E, D] and the correction [E]")
-    if ids.dtype != torch.int32 or ids.numel() != T * top or weights.numel() != T * top or dense.numel() != T * E:
+    if ids.dtype != torch.int32 or ids.numel() != T * top or weights.numel() != T * top or dense.numel() < T * real:
         raise KernelError("moe_route: outputs do not fit")
-    _check(lib().llb_moe_route(_ptr(x), _dt(x), _f32(w, "w"), _f32(correction, "correction"), T, D, E, top,
-                               1 if softmax else 0, 1 if renormalize else 0, ctypes.c_float(scale), _i32(ids, "ids"),
-                               _f32(weights, "weights"), _f32(dense, "dense"), _stream()))
+    if real < E and (identity_weight is None or identity_weight.numel() != T):
+        raise KernelError("moe_route: identity experts need identity_weight float32 [T]")
+    if gate_rows and (gate_out is None or gate_out.numel() != T * gate_rows):
+        raise KernelError("moe_route: gate rows need gate_out float32 [T, gate_rows]")
+    _check(lib().llb_moe_route_ex(_ptr(x), _dt(x), _f32(w, "w"), _f32(correction, "correction"), T, D, E, real, top,
+                                  1 if softmax else 0, 1 if renormalize else 0, ctypes.c_float(renorm_eps),
+                                  ctypes.c_float(scale), groups, keep, gate_rows, _i32(ids, "ids"), _f32(weights, "weights"),
+                                  _f32(dense, "dense"), _f32(identity_weight, "identity_weight"), _f32(gate_out, "gate_out"),
+                                  _stream()))
 
 
 def moe_scale(act: torch.Tensor, dense: torch.Tensor, num_experts: int, width: int) -> None:
@@ -708,18 +779,28 @@ def moe_gather(x: torch.Tensor, slot: torch.Tensor, top: int, xs: torch.Tensor) 
     _check(lib().llb_moe_gather(_ptr(x), _dt(x), _i32(slot, "slot"), T * top, top, D, _ptr(xs), _stream()))
 
 
-def moe_combine(y: torch.Tensor, slot: torch.Tensor, weights: torch.Tensor, residual: torch.Tensor) -> None:
-    """residual[t] += sum_k weights[t, k] * y[slot[t*top + k]] in float."""
+def moe_combine(y: Optional[torch.Tensor], slot: Optional[torch.Tensor], weights: Optional[torch.Tensor],
+                residual: torch.Tensor, x: Optional[torch.Tensor] = None,
+                identity_weight: Optional[torch.Tensor] = None) -> None:
+    """residual[t] += sum_k weights[t, k] * y[slot[t*top + k]] in float (a negative slot is skipped), then
+    ``+ identity_weight[t] * x[t]`` when identity experts exist.  ``y`` None: the identity term alone."""
     T, D = residual.shape
-    top = weights.shape[1]
-    if y.dtype != torch.float32 or y.shape[1] != D or slot.numel() != T * top or residual.dtype != torch.float32:
-        raise KernelError("moe_combine: sizes do not fit")
-    _check(lib().llb_moe_combine(_f32(y, "y"), _i32(slot, "slot"), _f32(weights, "weights"), T, top, D, _f32(residual, "residual"),
-                                 _stream()))
+    if residual.dtype != torch.float32:
+        raise KernelError("moe_combine: the stream is float32")
+    top = 0
+    if y is not None:
+        top = weights.shape[1]
+        if y.dtype != torch.float32 or y.shape[1] != D or slot.numel() != T * top:
+            raise KernelError("moe_combine: sizes do not fit")
+    if (x is None) != (identity_weight is None) or (x is not None and (tuple(x.shape) != (T, D) or identity_weight.numel() != T)):
+        raise KernelError("moe_combine: the identity term needs x [T, D] and float32 [T] weights")
+    _check(lib().llb_moe_combine_identity(_f32(y, "y"), _i32(slot, "slot"), _f32(weights, "weights"), T, top, D,
+                                          _f32(residual, "residual"), _ptr(x), _dt(x) if x is not None else 0,
+                                          _f32(identity_weight, "identity_weight"), _stream()))
 
 
 def moe_pairs(x: torch.Tensor, ids: torch.Tensor, w_gate_up: torch.Tensor, w_down_rows: torch.Tensor, act: torch.Tensor,
-              y: torch.Tensor) -> None:
+              y: torch.Tensor, glu=None) -> None:
     """The chosen experts of a few rows, pair by pair (bfloat16): ``y[t*top + k] = W_down[e] (silu(W_gate[e] x_t) *
     (W_up[e] x_t))`` with e = ids[t, k]; ``w_gate_up`` [E*2F, D] (gate and up rows interleaved), ``w_down_rows`` [E*D, F];
     ``act`` bfloat16 [T*top, F] scratch; ``y`` float32 [T*top, D]."""
@@ -730,8 +811,8 @@ def moe_pairs(x: torch.Tensor, ids: torch.Tensor, w_gate_up: torch.Tensor, w_dow
             w_gate_up.shape[1] != D or tuple(act.shape) != (pairs, F) or act.dtype != torch.bfloat16 or \
             tuple(y.shape) != (pairs, D) or y.dtype != torch.float32 or pairs != T * top:
         raise KernelError("moe_pairs: sizes or dtypes do not fit")
-    _check(lib().llb_moe_pairs(_ptr(x), _i32(ids, "ids"), pairs, top, D, F, _ptr(w_gate_up), _ptr(w_down_rows), _ptr(act),
-                               _f32(y, "y"), _stream()))
+    _check(lib().llb_moe_pairs_glu(_ptr(x), _i32(ids, "ids"), pairs, top, D, F, _ptr(w_gate_up), _ptr(w_down_rows), _ptr(act),
+                                   _f32(y, "y"), *_glu_args(glu), _stream()))
 
 
 def gemm_tcgen05_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, groups: int,

@@ -238,3 +238,133 @@ LLB_EXPORT int llb_qkv_prepare(const void* src, int dtype, long long row_stride,
         return llb_fail("qkv_prepare: unknown dtype %d", dtype);
     return llb_check_launch("qkv_prepare");
 }
+
+// ---------------------------------------------------------------------------------------------
+// head_prepare: what lies between a fused projection and the attention kernels when q and k are normed HEAD BY HEAD.
+//
+// src [T, row_stride] holds Hq query heads at q_off and Hk key heads at k_off, each hd wide.  Per head: an optional RMS
+// norm over the head's hd numbers with a weight [hd] shared by all heads (q_norm_w / k_norm_w, float or null), then the
+// rotation of the first rotary_dim dimensions.  Queries go to q_out, keys to the cache rows of the new tokens.
+//
+// q_maps = M > 1 spreads the queries for attention with M score maps a head: query head i (map i % M) is written as a
+// row of M * hd numbers that holds the head at offset (i % M) * hd and zeros elsewhere, so that against key rows that
+// hold a kv head's M maps side by side (k_cache [slots, Hk / M, M * hd], which is the same memory as [slots, Hk, hd]) the
+// dot product picks the query's own map, and M * H query heads share a kv head's value row in an ordinary grouped
+// attention.
+//
+// Values: v_mode 0 none; 1 the v_width numbers at v_off of src are copied to the slot's value row; 2 the value row is
+// the key row as projected (before norm and rotation), Hk * hd wide.
+namespace {
+
+template <typename T>
+__global__ void __launch_bounds__(256) head_prepare_kernel(
+    const T* __restrict__ src, long long row_stride, int q_off, int k_off, int v_off, int Hq, int Hk, int hd, int q_maps,
+    int v_mode, int v_width, const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w, float eps,
+    const int* __restrict__ positions, const float* __restrict__ inv_freq, int rotary_dim, int interleaved,
+    const int* __restrict__ slot_mapping, T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache) {
+    const int t = blockIdx.x;
+    const int lane = threadIdx.x & 31;
+    const int warps = (blockDim.x >> 5) * gridDim.y;
+    const int warp = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int pos = positions[t];
+    const T* row = src + (size_t)t * row_stride;
+    const int slot = slot_mapping ? slot_mapping[t] : -1;
+    const int half = rotary_dim / 2;
+    const int per_head = hd - half;
+    for (int head = warp; head < Hq + Hk; head += warps) {
+        const bool is_q = head < Hq;
+        const int h = is_q ? head : head - Hq;
+        if (!is_q && slot < 0) continue;
+        const T* s = row + (is_q ? q_off : k_off) + (size_t)h * hd;
+        const float* w = is_q ? q_norm_w : k_norm_w;
+        float inv = 1.0f;
+        if (w) {
+            float ss = 0.0f;
+            for (int d = lane; d < hd; d += 32) {
+                const float a = llb_to_float(s[d]);
+                ss += a * a;
+            }
+            inv = 1.0f / sqrtf(llb_warp_sum(ss) / (float)hd + eps);
+        }
+        T* dst;
+        if (is_q) {
+            T* wide = q_out + ((size_t)t * Hq + h) * ((size_t)q_maps * hd);
+            const int mine = h % q_maps;
+            for (int m = 0; m < q_maps; ++m) {
+                if (m == mine) continue;
+                for (int d = lane; d < hd; d += 32) wide[(size_t)m * hd + d] = llb_from_float<T>(0.0f);
+            }
+            dst = wide + (size_t)mine * hd;
+        } else {
+            dst = k_cache + ((size_t)slot * Hk + h) * hd;
+            if (v_mode == 2) {
+                T* vdst = v_cache + ((size_t)slot * Hk + h) * hd;
+                for (int d = lane; d < hd; d += 32) vdst[d] = s[d];
+            }
+        }
+        for (int j = lane; j < per_head; j += 32) {
+            if (j < half) {
+                const int ia = interleaved ? 2 * j : j;
+                const int ib = interleaved ? 2 * j + 1 : j + half;
+                float a = llb_to_float(s[ia]), b = llb_to_float(s[ib]);
+                if (w) {
+                    a = a * inv * w[ia];
+                    b = b * inv * w[ib];
+                }
+                const float angle = (float)pos * inv_freq[j];
+                const float c = cosf(angle), sn = sinf(angle);
+                dst[ia] = llb_from_float<T>(a * c - b * sn);
+                dst[ib] = llb_from_float<T>(b * c + a * sn);
+            } else {
+                const int d = rotary_dim + (j - half);
+                float a = llb_to_float(s[d]);
+                if (w) a = a * inv * w[d];
+                dst[d] = llb_from_float<T>(a);
+            }
+        }
+    }
+    if (slot >= 0 && v_mode == 1) {
+        const T* vsrc = row + v_off;
+        T* vdst = v_cache + (size_t)slot * v_width;
+        for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < v_width; i += gridDim.y * blockDim.x) vdst[i] = vsrc[i];
+    }
+}
+
+}  // namespace
+
+// q_out [T, Hq, q_maps * hd]; k_cache [slots, Hk * hd]; v_cache [slots, v_width] (v_mode 1) or [slots, Hk * hd] (v_mode 2);
+// slot_mapping [T] or null (then nothing is cached, Hk may be 0).
+LLB_EXPORT int llb_head_prepare(const void* src, int dtype, long long row_stride, int q_off, int k_off, int v_off, int T,
+                                int Hq, int Hk, int hd, int q_maps, int v_mode, int v_width, const float* q_norm_w,
+                                const float* k_norm_w, float eps, const int* positions, const float* inv_freq,
+                                int rotary_dim, int interleaved, const int* slot_mapping, void* q_out, void* k_cache,
+                                void* v_cache, cudaStream_t stream) {
+    if (T == 0) return 0;
+    LLB_REQUIRE(T > 0 && Hq >= 0 && Hk >= 0 && Hq + Hk > 0 && hd > 0 && q_maps >= 1 && src && positions,
+                "head_prepare: bad sizes");
+    LLB_REQUIRE(rotary_dim >= 0 && rotary_dim <= hd && rotary_dim % 2 == 0,
+                "head_prepare: rotary_dim %d must be even and at most the head's %d", rotary_dim, hd);
+    LLB_REQUIRE(rotary_dim == 0 || inv_freq != nullptr, "head_prepare: inv_freq is null");
+    LLB_REQUIRE(Hq == 0 || q_out != nullptr, "head_prepare: q_out is null");
+    LLB_REQUIRE(v_mode >= 0 && v_mode <= 2, "head_prepare: v_mode %d", v_mode);
+    LLB_REQUIRE(slot_mapping == nullptr || Hk == 0 || (k_cache != nullptr && (v_mode == 0 || v_cache != nullptr)),
+                "head_prepare: a cache plane is missing");
+    LLB_REQUIRE(v_mode != 1 || (v_off >= 0 && v_width > 0), "head_prepare: the values' columns are not given");
+    // a warp a head; few tokens (decoding): several blocks a token
+    const int heads = Hq + Hk;
+    int share = T >= 128 ? 1 : (heads + 7) / 8;
+    if (share > 8) share = 8;
+    const dim3 grid(T, share < 1 ? 1 : share);
+    if (dtype == LLB_F32)
+        head_prepare_kernel<float><<<grid, 256, 0, stream>>>(
+            (const float*)src, row_stride, q_off, k_off, v_off, Hq, Hk, hd, q_maps, v_mode, v_width, q_norm_w, k_norm_w, eps,
+            positions, inv_freq, rotary_dim, interleaved, slot_mapping, (float*)q_out, (float*)k_cache, (float*)v_cache);
+    else if (dtype == LLB_BF16)
+        head_prepare_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(
+            (const __nv_bfloat16*)src, row_stride, q_off, k_off, v_off, Hq, Hk, hd, q_maps, v_mode, v_width, q_norm_w,
+            k_norm_w, eps, positions, inv_freq, rotary_dim, interleaved, slot_mapping, (__nv_bfloat16*)q_out,
+            (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache);
+    else
+        return llb_fail("head_prepare: unknown dtype %d", dtype);
+    return llb_check_launch("head_prepare");
+}

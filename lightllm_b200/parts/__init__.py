@@ -4,6 +4,8 @@ from .attention import AttentionMixer
 from .block import Block, build_part
 from .conv_attention import ConvAttentionMixer
 from .delta import ChannelDeltaMixer
+from .differential_attention import DifferentialAttentionMixer
+from .sink_attention import KeyValuedAttentionMixer
 from .moe import RoutedExperts
 from .stream import StreamReinjection, StreamStepVector
 from .input_conv import CausalInputConv
@@ -21,4 +23,5 @@ __all__ = ["CacheView", "FeedForward", "Mixer", "Norm", "Part", "PositionEncodin
            "build_part", "LMHead", "TokenEmbedding", "GatedMLP", "RMSNorm", "LayerNorm", "GatedAttentionMixer",
            "LatentAttentionMixer", "RetentionMixer", "NoPositionEncoding", "RotaryEmbedding", "ConvAttentionMixer",
            "ChannelDeltaMixer", "RoutedExperts", "StreamReinjection", "StreamStepVector", "CausalInputConv",
-           "MixedHeadsAttention", "MatrixMemoryMixer", "JoinedMixers"]
+           "MixedHeadsAttention", "MatrixMemoryMixer", "JoinedMixers", "DifferentialAttentionMixer",
+           "KeyValuedAttentionMixer"]

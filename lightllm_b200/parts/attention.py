@@ -51,7 +51,7 @@ class AttentionMixer(Mixer):
                  position: Optional[PartSpec] = None, qkv_bias: bool = True, out_bias: bool = False,
                  window: Optional[int] = None, scale: Optional[float] = None,
                  names: Optional[Dict[str, str]] = None, weight_suffix: str = ".weight",
-                 v_head_dim: Optional[int] = None, chunk: Optional[int] = None):
+                 v_head_dim: Optional[int] = None, chunk: Optional[int] = None, cache_window: Optional[int] = None):
         if window and chunk:
             raise ValueError("an attention mixer takes a window or a chunk, not both")
         if num_heads % num_kv_heads:
@@ -69,8 +69,14 @@ class AttentionMixer(Mixer):
         # kernels apply every query head's weights to the values of EVERY kv head, out is [T, heads, cross, v_head_dim].
         # out may be float32 under bfloat16 inputs.
         self.value_cross = 1
+        # A soft cap on the scores (set by mixers that have one): score <- softcap * tanh(score / softcap) before the
+        # softmax; sinks are not capped.
+        self.softcap: Optional[float] = None
         self.weight_suffix = weight_suffix
         self.window = window
+        # How many of the latest keys the cache plane keeps, when other run entries read this one's plane through windows
+        # of their own (0: every key); ``None``: what this mixer's own window needs.
+        self.cache_window = cache_window
         self.chunk = int(chunk) if chunk else None
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
         self.names = {"q": "q_proj", "k": "k_proj", "v": "v_proj", "o": "o_proj"}
@@ -92,7 +98,8 @@ class AttentionMixer(Mixer):
 
     def cache_spec(self) -> CacheSpec:
         vd = 0 if self.values_in_keys else (None if self.v_head_dim == self.head_dim else self.v_head_dim)
-        return CacheSpec(kv=KVSpec(self.num_kv_heads, self.head_dim, self.window, vd, self.chunk))
+        keep = self.window if self.cache_window is None else (self.cache_window or None)
+        return CacheSpec(kv=KVSpec(self.num_kv_heads, self.head_dim, keep, vd, self.chunk))
 
     def kernel_window(self) -> int:
         """The mask as the attention kernels take it: a window > 0, minus the chunk, or 0 for every earlier key."""
@@ -227,7 +234,7 @@ class AttentionMixer(Mixer):
         ``prepare`` when the engine runs it, so that the index arrays travel with the step's metadata)."""
         window = self.kernel_window()
         # the tensor-core kernels take values as wide as the keys (sinks and values in the key rows included)
-        plain = self.v_head_dim == self.head_dim
+        plain = self.v_head_dim == self.head_dim and not self.softcap
         cross = self.value_cross
         key = ("attention_plan", self.num_heads, self.num_kv_heads, self.head_dim, window, dtype, plain, cross)
         plan = ctx.memo.get(key)
@@ -308,7 +315,7 @@ class AttentionMixer(Mixer):
             if pos_key is None:
                 return None
         return ("attention", self.num_heads, self.num_kv_heads, self.head_dim, self.v_head_dim, self.kernel_window(),
-                self.sinks is not None, self.values_in_keys, self.value_cross, pos_key)
+                self.sinks is not None, self.values_in_keys, self.value_cross, bool(self.softcap), pos_key)
 
     def prepare(self, ctx, cache=None) -> None:
         self._plan(ctx, ctx.dtype)
@@ -362,7 +369,7 @@ class AttentionMixer(Mixer):
                                   dtype=torch.float32, device=q.device)
         ops.paged_attention_simt(q, cache.k, cache.k if self.values_in_keys else cache.v, out, tile_span, tile_q0, ntiles,
                                  *common, bq, nsplit, scratch, v_head_dim=hdv, sinks=self.sinks,
-                                 v_shared=self.value_cross > 1)
+                                 v_shared=self.value_cross > 1, softcap=self.softcap or 0.0)
 
 
 register_part("mixer", "attention", AttentionMixer)

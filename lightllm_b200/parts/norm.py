@@ -13,22 +13,27 @@ from .base import Norm
 
 class RMSNorm(Norm):
     """``y = x / sqrt(mean(x^2) + eps) * weight`` with the statistics in float32
-    (src/ops/norm.cu:19-23,48-54).  ``weight_name`` is the full checkpoint name."""
+    (src/ops/norm.cu:19-23,48-54).  ``weight_name`` is appended to ``prefix`` with a dot (an empty one makes the prefix
+    itself the weight's name).  ``one_plus``: the checkpoint stores the weight around zero and the norm multiplies by
+    ``1 + w``; the sum is made once, in float32, when the model is bound."""
 
     graph_safe = True
 
-    def __init__(self, prefix: str, hidden_size: int, eps: float, weight_name: str = "weight"):
-        self.name = f"{prefix}.{weight_name}" if prefix else weight_name
+    def __init__(self, prefix: str, hidden_size: int, eps: float, weight_name: str = "weight", one_plus: bool = False):
+        self.name = (f"{prefix}.{weight_name}" if weight_name else prefix) if prefix else weight_name
         self.hidden_size = hidden_size
         self.eps = float(eps)
+        self.one_plus = bool(one_plus)
         self.weight = None
         self.out_dtype = torch.float32
 
     def weight_specs(self) -> List[WeightSpec]:
-        return [WeightSpec(self.name, (self.hidden_size,), init=("one_plus_normal", 0.01))]
+        return [WeightSpec(self.name, (self.hidden_size,), init=("normal", 0.1) if self.one_plus else ("one_plus_normal", 0.01))]
 
     def bind(self, tensors: Dict[str, torch.Tensor], dtype, device) -> None:
         self.weight = tensors[self.name]
+        if self.one_plus:
+            self.weight = (1.0 + self.weight.float()).contiguous()
         self.out_dtype = dtype
 
     def rms_parameters(self):
