@@ -2,7 +2,7 @@
 float64 torch on the CPU.  It shares no code with the engine; the tests compare the engine with it.
 
 ``tensors`` maps checkpoint names to tensors; ``cfg`` is the config.json dictionary.  Every function takes whole
-sequences (positions 0 .. T-1 of one request) and loops over rows, heads and keys.
+sequences (positions 0 .. T-1 of one request) and loops over rows and heads.
 """
 from __future__ import annotations
 
@@ -57,15 +57,15 @@ def windowed_attention(q, k, v, scale: float, window: Optional[int], softcap: Op
     for h in range(H):
         g = h // (H // G)
         for i in range(T):
-            js = list(visible(i, window))
-            s = torch.stack([(q[i, h] * k[j, g]).sum() * scale for j in js])
+            js = visible(i, window)
+            lo, hi = js.start, js.stop
+            s = (k[lo:hi, g] @ q[i, h]) * scale                     # one score a visible key
             if softcap:
                 s = softcap * torch.tanh(s / softcap)
             m = s.max() if sinks is None else torch.maximum(s.max(), sinks[h])
             e = torch.exp(s - m)
             den = e.sum() + (torch.exp(sinks[h] - m) if sinks is not None else 0.0)
-            for w, j in zip(e / den, js):
-                out[i, h] += w * v[j, g]
+            out[i, h] = (e / den) @ v[lo:hi, g]
     return out
 
 
