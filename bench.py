@@ -5,7 +5,7 @@
     python bench.py --sizes 1.5b|7b          (the larger sizes of the family: a line of their own)
     python bench.py [--sizes ..] --only decode|prefill [--prompt-len N]     (one part, at another context length)
     python bench.py --only small-mixed       (the steps of a loaded server: a 16-token portion beside decoded tokens)
-    python bench.py --design kudadra|bulitar|kuzezen [--sizes 1.5b] [--layers L]     (another design beside Qwen2 at equal sizes)
+    python bench.py --design kudadra|bulitar|kuzezen|fedirax [--sizes 1.5b] [--layers L]     (another design beside Qwen2 at equal sizes)
 
 Prints one JSON line.  ``value`` is decoded tokens a second over K timed decode steps of a
 batch of 8 requests that each hold a 2,048-token prompt (random weights, random token ids),
@@ -384,6 +384,40 @@ def kuzezen_config(base: dict, layers: int, ff: bool = True) -> dict:
             "layers": [{"type": "parallel", "mixer": mixer, "mlp": mlp} for _ in range(max(1, inner + layers - 2 * inner))]}
 
 
+def fedirax_config(base: dict, layers: int, kinds=("attention_2", "attention"), experts: int = 8, top: int = 2,
+                   share: bool = True) -> dict:
+    """A Fedirax model with the width, head count, head size and vocabulary of a Qwen2 configuration.  Its layers cycle
+    through ``kinds``: differential layers with the base's heads, two maps of half the base's head size each (so a key
+    row and a value row are as wide as the base's) and, from the third on, keys and values read from the first such
+    layer (``share``); keys-as-values layers with the base's heads, a cap of 30 and a sink.  Windows of 1,024, full
+    rotation.  ``experts`` experts of which ``top`` are chosen, each as wide as the dense feed-forward divided by
+    ``top``, two identity experts beside them, two groups of which one is kept, and a shared expert of a quarter of the
+    dense width."""
+    D, H, G = base["hidden_size"], base["num_attention_heads"], base["num_key_value_heads"]
+    hd = base.get("head_dim", D // H)
+    mixers = {
+        "attention": {"heads": H, "kv_heads": G, "dim": hd, "vdim": hd, "mask": {"size": 1024}, "scale": hd ** -0.5,
+                      "softcap": 30.0, "rot": {"dims": hd, "base": 500000.0}},
+        "attention_2": {"heads": H, "kv_heads": G, "dim": hd // 2, "vdim": hd, "mask": {"size": 1024},
+                        "scale": (hd // 2) ** -0.5, "diff": 0.3, "rot": {"dims": hd // 2, "base": 250000.0}},
+    }
+    mlp = {"kind": "moe", "expert": {"ff": base["intermediate_size"] // top, "limit": 7.0},
+           "router": {"experts": experts, "top": top, "scale": 2.0, "identity": 2, "groups": {"count": 2, "keep": 1}},
+           "shared": {"ff": base["intermediate_size"] // 4, "limit": 7.0}}
+    out, first = [], None
+    for i in range(layers):
+        kind = kinds[i % len(kinds)]
+        mixer = dict(mixers[kind])
+        if kind == "attention_2":
+            if first is None:
+                first = i
+            elif share and sum(l["type"] == kind for l in out) >= 2:
+                mixer["kv_from"] = first
+        out.append({"type": kind, "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Fedirax", "vocab": base["vocab_size"], "width": D, "embedding": {"scale": 3.0},
+            "norm": {"eps": 1e-6}, "layers": out}
+
+
 def run_design(name: str, sizes: str, layers: int, steps: int, warmup: int, only=None) -> int:
     """Prefill of one 2,048-token prompt and decode at batch 1 / 8 / 64 over 2,048-token contexts for another design:
     its kinds of layer in turn, each kind alone, and Qwen2 with as many layer runs of the same width, feed-forward,
@@ -398,6 +432,12 @@ def run_design(name: str, sizes: str, layers: int, steps: int, warmup: int, only
         for kind in ("attention", "channel_delta"):
             arms[f"bulitar/{kind}"] = bulitar_config(base, layers, (kind,))
         arms["bulitar/every expert chosen"] = bulitar_config(base, layers, experts=2, top=2)
+    elif name == "fedirax":
+        # beside Qwen2 and beside the engine's closest design, Bulitar's attention layers over routed experts
+        arms = {"qwen2": base, "bulitar/attention": bulitar_config(base, layers, ("attention",)),
+                "fedirax": fedirax_config(base, layers)}
+        for kind in ("attention", "attention_2"):
+            arms[f"fedirax/{kind}"] = fedirax_config(base, layers, (kind,), share=False)
     elif name == "kuzezen":
         arms = {"qwen2": base, "kuzezen": kuzezen_config(base, layers),
                 "kuzezen/no feed-forward": kuzezen_config(base, layers, ff=False)}
@@ -441,7 +481,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=QWEN25_05B["num_hidden_layers"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (for profiling runs)")
-    ap.add_argument("--design", choices=["kudadra", "bulitar", "kuzezen"], default=None,
+    ap.add_argument("--design", choices=["kudadra", "bulitar", "kuzezen", "fedirax"], default=None,
                     help="measure another design beside Qwen2 at equal sizes (0.5B sizes, or --sizes; --layers, default 6; "
                          "--only names arms, e.g. kudadra,qwen2): a line of its own, not the bench record")
     ap.add_argument("--sizes", choices=["1.5b", "7b"], default=None,

@@ -39,6 +39,7 @@ struct DecodeParams {
     const int* block_table;
     int max_pages, page_size, Hq, Hkv, window, nsplit;
     float scale_log2e;
+    float cap_log2e, inv_cap;      // a soft cap on the scores: cap * log2(e) and scale / cap (0: no cap)
     float* part_acc;               // [tiles, Hkv, nsplit, G, HD]
     float* part_ml;                // [tiles, Hkv, nsplit, G, 2]   (m in base-2 units, l)
     const float* sinks;            // [Hq] or null: exp(sinks[h]) joins head h's softmax denominator once
@@ -206,7 +207,15 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_decode_mma_kernel(DecodePar
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int key = kb + i * 8 + c0 + (e & 1);
-                const float v = key < khi ? s[i][e] * p.scale_log2e : -INFINITY;
+                float v = -INFINITY;
+                if (key < khi) {
+                    if (p.cap_log2e > 0.0f) {          // cap * tanh(s * scale / cap), tanh(x) = 1 - 2 / (1 + e^(2x))
+                        const float x = fminf(s[i][e] * p.inv_cap, 40.0f);
+                        v = (1.0f - __fdividef(2.0f, 1.0f + fast_exp2(x * 2.8853900817779268f))) * p.cap_log2e;
+                    } else {
+                        v = s[i][e] * p.scale_log2e;
+                    }
+                }
                 s[i][e] = v;
                 mt[e >> 1] = fmaxf(mt[e >> 1], v);
             }
@@ -505,11 +514,13 @@ LLB_EXPORT int llb_paged_decode_mma_cluster_splits() { return CLUSTER_MAX_SPLITS
 // (values read out of the key rows).
 // cross > 1 (then = Hkv, and no sinks): crossed values, out is [T, Hq, cross, hd] and holds every query head's
 // weights applied to the values of every kv head; scratch counts Hq * cross heads.  out_float: out is float, not bf16.
-LLB_EXPORT int llb_paged_decode_mma_cross(const void* q, const void* k_cache, const void* v_cache, void* out,
-                                          const int* tile_span, const int* tile_q0, int num_tiles, const int* span_row,
-                                          const int* span_pos, const int* block_table, int max_pages, int page_size,
-                                          int Hq, int Hkv, int hd, int window, float scale, int nsplit, float* scratch,
-                                          const float* sinks, int cross, int out_float, cudaStream_t stream) {
+// softcap > 0: every score (after `scale`) becomes softcap * tanh(score / softcap) before the softmax; sinks are not capped.
+LLB_EXPORT int llb_paged_decode_mma_capped(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                           const int* tile_span, const int* tile_q0, int num_tiles, const int* span_row,
+                                           const int* span_pos, const int* block_table, int max_pages, int page_size,
+                                           int Hq, int Hkv, int hd, int window, float scale, float softcap, int nsplit,
+                                           float* scratch, const float* sinks, int cross, int out_float,
+                                           cudaStream_t stream) {
     if (num_tiles == 0) return 0;
     LLB_REQUIRE(cross == 1 || (cross == Hkv && sinks == nullptr),
                 "decode attention: crossed values take cross = the number of kv heads (%d), got %d, and no sinks", Hkv, cross);
@@ -525,6 +536,8 @@ LLB_EXPORT int llb_paged_decode_mma_cross(const void* q, const void* k_cache, co
     p.out = (__nv_bfloat16*)out; p.tile_span = tile_span; p.tile_q0 = tile_q0; p.span_row = span_row; p.span_pos = span_pos;
     p.block_table = block_table; p.max_pages = max_pages; p.page_size = page_size; p.Hq = Hq; p.Hkv = Hkv;
     p.window = window; p.nsplit = nsplit; p.scale_log2e = scale * 1.4426950408889634f;
+    p.cap_log2e = softcap > 0.0f ? softcap * 1.4426950408889634f : 0.0f;
+    p.inv_cap = softcap > 0.0f ? scale / softcap : 0.0f;
     p.sinks = sinks;
     p.cross = cross;
     p.out_f32 = out_float ? (float*)out : nullptr;
@@ -533,6 +546,16 @@ LLB_EXPORT int llb_paged_decode_mma_cross(const void* q, const void* k_cache, co
     p.part_ml = scratch ? scratch + (size_t)num_tiles * Hkv * cross * nsplit * G * hd : nullptr;
     if (hd == 64) return launch<64>(p, num_tiles, stream);
     return launch<128>(p, num_tiles, stream);
+}
+
+LLB_EXPORT int llb_paged_decode_mma_cross(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                          const int* tile_span, const int* tile_q0, int num_tiles, const int* span_row,
+                                          const int* span_pos, const int* block_table, int max_pages, int page_size,
+                                          int Hq, int Hkv, int hd, int window, float scale, int nsplit, float* scratch,
+                                          const float* sinks, int cross, int out_float, cudaStream_t stream) {
+    return llb_paged_decode_mma_capped(q, k_cache, v_cache, out, tile_span, tile_q0, num_tiles, span_row, span_pos,
+                                       block_table, max_pages, page_size, Hq, Hkv, hd, window, scale, 0.0f, nsplit, scratch,
+                                       sinks, cross, out_float, stream);
 }
 
 LLB_EXPORT int llb_paged_decode_mma_sinks(const void* q, const void* k_cache, const void* v_cache, void* out,

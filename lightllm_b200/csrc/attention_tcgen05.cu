@@ -62,11 +62,20 @@ __device__ __forceinline__ float row_max(uint32_t tmem_s, int c_begin, int c_lo,
     }
     return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
 }
+// A soft-capped score in base-2 units: cap * tanh(s * scale / cap) * log2(e), with tanh(x) = 1 - 2 / (1 + e^(2x)) from
+// the fast exponential and division (an absolute error of about 1e-7 in tanh, 1e-7 * cap in the score).  Minus
+// infinity (a masked key) stays minus infinity.
+__device__ __forceinline__ float capped_score(float s, float inv_cap, float cap_log2e) {
+    const float x = fminf(s * inv_cap, 40.0f);
+    const float t = 1.0f - __fdividef(2.0f, 1.0f + fast_exp2(x * 2.8853900817779268f));
+    return s == -INFINITY ? -INFINITY : t * cap_log2e;
+}
 // p = 2^(s*c - m) of this thread's 64 scores of the row, written as bf16 into the swizzled A-operand tiles; returns
 // their sum (float, before rounding).  Row r, 16-byte chunk q of a 128-byte row lands at chunk q ^ (r & 7).
-template <bool MASKED>
+// CAPPED: c_scale is scale / cap and the score in base-2 units is capped_score(s, c_scale, cap_log2e).
+template <bool MASKED, bool CAPPED = false>
 __device__ __forceinline__ float row_probs(uint32_t tmem_s, uint8_t* p_s, int r, int c_begin, float c_scale, float m_use,
-                                           int c_lo, int c_hi) {
+                                           int c_lo, int c_hi, float cap_log2e = 0.0f) {
     float l0 = 0.0f, l1 = 0.0f;
 #pragma unroll 1
     for (int c = c_begin; c < c_begin + 2; ++c) {
@@ -82,8 +91,14 @@ __device__ __forceinline__ float row_probs(uint32_t tmem_s, uint8_t* p_s, int r,
             uint32_t w[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const float p0 = fast_exp2(fmaf(s[q * 8 + 2 * e], c_scale, -m_use));
-                const float p1 = fast_exp2(fmaf(s[q * 8 + 2 * e + 1], c_scale, -m_use));
+                float p0, p1;
+                if (CAPPED) {
+                    p0 = fast_exp2(capped_score(s[q * 8 + 2 * e], c_scale, cap_log2e) - m_use);
+                    p1 = fast_exp2(capped_score(s[q * 8 + 2 * e + 1], c_scale, cap_log2e) - m_use);
+                } else {
+                    p0 = fast_exp2(fmaf(s[q * 8 + 2 * e], c_scale, -m_use));
+                    p1 = fast_exp2(fmaf(s[q * 8 + 2 * e + 1], c_scale, -m_use));
+                }
                 l0 += p0;
                 l1 += p1;
                 const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
@@ -106,6 +121,7 @@ struct AttnTcParams {
     const int* block_table;    // [S, max_pages]
     int max_pages, page_size, Hq, Hkv, window, num_slots, num_items;
     float scale_log2e;         // scale * log2(e): scores are kept in base-2 units
+    float cap_log2e, inv_cap;  // a soft cap on the scores: cap * log2(e) and scale / cap (0: no cap), see capped_score
     uint32_t dynamic_smem_bytes;
     // Optional cut of a tile's key range into work items, so that long rows do not set the kernel's time:
     // item i covers key tiles [tile_k0[i], tile_k0[i] + tile_nk[i]) of its query tile and, when tile_part[i] >= 0,
@@ -165,7 +181,9 @@ __device__ __forceinline__ void named_barrier(int id, int threads) {
 // The roles meet on mbarriers (data arrived, buffers free, tensor-core work done; every wait is bounded) and on
 // named barriers among softmax and MMA warps.  After a wait has run out every role still walks through all its
 // items and barriers, without copies, tensor-core work or stores, so that no barrier is left waiting.
-template <int HD>
+// CAP: the scores carry a soft cap (p.cap_log2e, p.inv_cap); a kernel of its own, so that the plain one keeps its
+// registers.
+template <int HD, bool CAP>
 __global__ void __launch_bounds__(NUM_THREADS, HD <= 64 ? 2 : 1)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, const AttnTcParams p) {
@@ -388,12 +406,17 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 else m_tile = row_max<true>(tmem_s, 2 * half, c_lo, c_hi);
                 xch[half][r] = __float2bfloat16_ru(m_tile);      // rewritten only after the barriers further down
                 named_barrier(BAR_SOFTMAX, NUM_SOFTMAX);
-                m_tile = fmaxf(__bfloat162float(xch[0][r]), __bfloat162float(xch[1][r])) * p.scale_log2e;   // the scale is positive
+                m_tile = fmaxf(__bfloat162float(xch[0][r]), __bfloat162float(xch[1][r]));
+                // the scale is positive and the cap grows with the score: the largest raw score gives the largest capped one
+                m_tile = CAP ? capped_score(m_tile, p.inv_cap, p.cap_log2e) : m_tile * p.scale_log2e;
                 const float m_new = fmaxf(m_run, m_tile);
                 const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;      // nothing visible yet: all p are 0
                 const float corr = (m_run == -INFINITY) ? 0.0f : fast_exp2(m_run - m_use);
                 float l_tile;
-                if (interior) l_tile = row_probs<false>(tmem_s, p_s, r, 2 * half, p.scale_log2e, m_use, c_lo, c_hi);
+                if (CAP) {
+                    if (interior) l_tile = row_probs<false, true>(tmem_s, p_s, r, 2 * half, p.inv_cap, m_use, c_lo, c_hi, p.cap_log2e);
+                    else l_tile = row_probs<true, true>(tmem_s, p_s, r, 2 * half, p.inv_cap, m_use, c_lo, c_hi, p.cap_log2e);
+                } else if (interior) l_tile = row_probs<false>(tmem_s, p_s, r, 2 * half, p.scale_log2e, m_use, c_lo, c_hi);
                 else l_tile = row_probs<true>(tmem_s, p_s, r, 2 * half, p.scale_log2e, m_use, c_lo, c_hi);
                 l_run = l_run * corr + l_tile;
                 m_run = m_new;
@@ -536,7 +559,7 @@ int make_map(const void* ptr, long long rows, long long cols, int box_rows, CUte
     return make_map_bf16(ptr, rows, cols, box_rows, out);
 }
 
-template <int HD>
+template <int HD, bool CAP>
 int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnTcParams& p, int num_tiles,
            cudaStream_t stream) {
     constexpr int KB = HD / 64;
@@ -545,7 +568,7 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
     constexpr size_t smem = (size_t)(KB + 4 * KB + 2) * 128 * 128 + 1024 - 592;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel<HD, CAP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)smem);
         if (e != cudaSuccess) return llb_fail("attention_tcgen05: cannot opt in to %zu bytes of shared memory: %s", smem,
                                               cudaGetErrorString(e));
@@ -575,7 +598,7 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, attention_tcgen05_kernel<HD>, mq, mk, mv, pp);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, attention_tcgen05_kernel<HD, CAP>, mq, mk, mv, pp);
     if (e != cudaSuccess) return llb_fail("attention_tcgen05: launch failed: %s", cudaGetErrorString(e));
     return llb_check_launch("attention_tcgen05");
 }
@@ -596,14 +619,15 @@ LLB_EXPORT int llb_attention_tcgen05_supports(int hd, int page_size) {
 // tiles, by the merge for cut ones: give the merge the same pointer).  v_cache may be k_cache.
 // cross > 1 (then = Hkv, and no sinks): crossed values.  out is float [T, Hq, cross, hd] and holds every query head's
 // weights applied to the values of every kv head; part_scratch and the merge count Hq * cross heads.
-LLB_EXPORT int llb_paged_attention_tcgen05_cross(const void* q, const void* k_cache, const void* v_cache, void* out, int T,
-                                                 const int* tile_span, const int* tile_q0, int num_tiles,
-                                                 const int* span_row, const int* span_len, const int* span_pos,
-                                                 const int* block_table, int max_pages, int page_size, int num_slots,
-                                                 int Hq, int Hkv, int hd, int window, float scale, const int* tile_k0,
-                                                 const int* tile_nk, const int* tile_part, float* part_scratch,
-                                                 int num_parts, const float* sinks, int cross, int out_float,
-                                                 int* error_flag, cudaStream_t stream) {
+// softcap > 0: every score (after `scale`) becomes softcap * tanh(score / softcap) before the softmax; sinks are not capped.
+LLB_EXPORT int llb_paged_attention_tcgen05_capped(const void* q, const void* k_cache, const void* v_cache, void* out, int T,
+                                                  const int* tile_span, const int* tile_q0, int num_tiles,
+                                                  const int* span_row, const int* span_len, const int* span_pos,
+                                                  const int* block_table, int max_pages, int page_size, int num_slots,
+                                                  int Hq, int Hkv, int hd, int window, float scale, float softcap,
+                                                  const int* tile_k0, const int* tile_nk, const int* tile_part,
+                                                  float* part_scratch, int num_parts, const float* sinks, int cross,
+                                                  int out_float, int* error_flag, cudaStream_t stream) {
     if (num_tiles == 0) return 0;
     LLB_REQUIRE(cross == 1 || (cross == Hkv && sinks == nullptr),
                 "attention_tcgen05: crossed values take cross = the number of kv heads (%d), got %d, and no sinks", Hkv, cross);
@@ -627,12 +651,30 @@ LLB_EXPORT int llb_paged_attention_tcgen05_cross(const void* q, const void* k_ca
     p.tile_span = tile_span; p.tile_q0 = tile_q0; p.span_row = span_row; p.span_len = span_len; p.span_pos = span_pos;
     p.block_table = block_table; p.max_pages = max_pages; p.page_size = page_size; p.Hq = Hq; p.Hkv = Hkv;
     p.window = window; p.num_slots = num_slots; p.scale_log2e = scale * 1.4426950408889634f; p.error_flag = error_flag;
+    p.cap_log2e = softcap > 0.0f ? softcap * 1.4426950408889634f : 0.0f;
+    p.inv_cap = softcap > 0.0f ? scale / softcap : 0.0f;
     p.tile_k0 = tile_k0; p.tile_nk = tile_nk; p.tile_part = tile_part;
     p.sinks = sinks;
     p.part_o = part_scratch;
     p.part_ml = part_scratch ? part_scratch + (size_t)num_parts * Hq * cross * BQ * hd : nullptr;
-    if (hd == 64) return launch<64>(mq, mk, mv, p, num_tiles, stream);
-    return launch<128>(mq, mk, mv, p, num_tiles, stream);
+    if (p.cap_log2e > 0.0f)
+        return hd == 64 ? launch<64, true>(mq, mk, mv, p, num_tiles, stream) : launch<128, true>(mq, mk, mv, p, num_tiles, stream);
+    if (hd == 64) return launch<64, false>(mq, mk, mv, p, num_tiles, stream);
+    return launch<128, false>(mq, mk, mv, p, num_tiles, stream);
+}
+
+LLB_EXPORT int llb_paged_attention_tcgen05_cross(const void* q, const void* k_cache, const void* v_cache, void* out, int T,
+                                                 const int* tile_span, const int* tile_q0, int num_tiles,
+                                                 const int* span_row, const int* span_len, const int* span_pos,
+                                                 const int* block_table, int max_pages, int page_size, int num_slots,
+                                                 int Hq, int Hkv, int hd, int window, float scale, const int* tile_k0,
+                                                 const int* tile_nk, const int* tile_part, float* part_scratch,
+                                                 int num_parts, const float* sinks, int cross, int out_float,
+                                                 int* error_flag, cudaStream_t stream) {
+    return llb_paged_attention_tcgen05_capped(q, k_cache, v_cache, out, T, tile_span, tile_q0, num_tiles, span_row, span_len,
+                                              span_pos, block_table, max_pages, page_size, num_slots, Hq, Hkv, hd, window,
+                                              scale, 0.0f, tile_k0, tile_nk, tile_part, part_scratch, num_parts, sinks,
+                                              cross, out_float, error_flag, stream);
 }
 
 LLB_EXPORT int llb_paged_attention_tcgen05_sinks(const void* q, const void* k_cache, const void* v_cache, void* out, int T,

@@ -957,12 +957,13 @@ def paged_attention_tcgen05(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
                             span_row: torch.Tensor, span_len: torch.Tensor, span_pos: torch.Tensor,
                             block_table: torch.Tensor, max_pages: int, page_size: int,
                             num_heads: int, num_kv_heads: int, head_dim: int, window: int, scale: float,
-                            cut=None, sinks: Optional[torch.Tensor] = None, cross: int = 1) -> None:
+                            cut=None, sinks: Optional[torch.Tensor] = None, cross: int = 1, softcap: float = 0.0) -> None:
     """Tensor-core attention of the listed tiles (128 query rows each) over the requests' pages; bf16.
     ``sinks`` float32 [num_heads]: ``exp(sinks[h])`` joins head h's softmax denominator once; ``v_cache`` may be
     ``k_cache`` itself (values read out of the key rows).  ``cross`` = ``num_kv_heads`` (> 1): crossed values, ``out``
     is [T, num_heads, cross, head_dim] and holds every query head's weights applied to the values of every kv
-    head; ``cut`` must then have been made for ``num_heads * cross`` heads.  ``out`` may be float32.
+    head; ``cut`` must then have been made for ``num_heads * cross`` heads.  ``out`` may be float32.  ``softcap`` > 0: a
+    score becomes ``softcap * tanh(score / softcap)`` before the softmax.
 
     ``cut`` = ``(tile_k0, tile_nk, tile_part, num_parts, merge_span, merge_q0, merge_first, merge_count,
     num_merge)`` cuts long key ranges into items (see ``StepContext.attention_items``); the partial results
@@ -984,12 +985,12 @@ def paged_attention_tcgen05(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
                                   device=q.device)
     if sinks is not None and (sinks.dtype != torch.float32 or sinks.numel() != num_heads):
         raise KernelError(f"attention_tcgen05: sinks must be float32 [{num_heads}]")
-    _check(lib().llb_paged_attention_tcgen05_cross(
+    _check(lib().llb_paged_attention_tcgen05_capped(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), T,
         _i32(tile_span, "tile_span"), _i32(tile_q0, "tile_q0"), num_tiles,
         _i32(span_row, "span_row"), _i32(span_len, "span_len"), _i32(span_pos, "span_pos"),
         _i32(block_table, "block_table"), max_pages, page_size, num_slots, num_heads, num_kv_heads, head_dim,
-        window, ctypes.c_float(scale), _i32(k0, "tile_k0"), _i32(nk, "tile_nk"), _i32(part, "tile_part"),
+        window, ctypes.c_float(scale), ctypes.c_float(softcap or 0.0), _i32(k0, "tile_k0"), _i32(nk, "tile_nk"), _i32(part, "tile_part"),
         _ptr(scratch), num_parts, _ptr(sinks), cross, out_float, _ptr(async_error_flag(q.device)), _stream()))
     if cut is not None and num_parts:
         _check(lib().llb_attention_tcgen05_merge_cross(
@@ -1033,10 +1034,10 @@ def paged_decode_mma(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
                      span_pos: torch.Tensor, block_table: torch.Tensor, max_pages: int, page_size: int,
                      num_heads: int, num_kv_heads: int, head_dim: int, window: int, scale: float,
                      nsplit: int = 1, scratch: Optional[torch.Tensor] = None,
-                     sinks: Optional[torch.Tensor] = None, cross: int = 1) -> None:
+                     sinks: Optional[torch.Tensor] = None, cross: int = 1, softcap: float = 0.0) -> None:
     """Tensor-core decode attention: one query row per tile over its request's pages; bf16.  ``nsplit`` cuts
     each request's keys; up to :func:`decode_mma_cluster_splits` the pieces are merged inside the kernel.
-    ``sinks``, ``v_cache is k_cache``, ``cross`` (crossed values) and a float32 ``out`` as
+    ``sinks``, ``v_cache is k_cache``, ``cross`` (crossed values), ``softcap`` and a float32 ``out`` as
     :func:`paged_attention_tcgen05`."""
     if sinks is not None and (sinks.dtype != torch.float32 or sinks.numel() != num_heads):
         raise KernelError(f"decode attention: sinks must be float32 [{num_heads}]")
@@ -1049,10 +1050,11 @@ def paged_decode_mma(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
         need = attention_scratch_floats(num_tiles, num_heads * cross, head_dim, 1, nsplit)
         if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need:
             raise KernelError(f"decode attention: nsplit={nsplit} needs {need} floats of scratch")
-    _check(lib().llb_paged_decode_mma_cross(
+    _check(lib().llb_paged_decode_mma_capped(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _i32(tile_span, "tile_span"), _i32(tile_q0, "tile_q0"),
         num_tiles, _i32(span_row, "span_row"), _i32(span_pos, "span_pos"), _i32(block_table, "block_table"),
-        max_pages, page_size, num_heads, num_kv_heads, head_dim, window, ctypes.c_float(scale), nsplit,
+        max_pages, page_size, num_heads, num_kv_heads, head_dim, window, ctypes.c_float(scale),
+        ctypes.c_float(softcap or 0.0), nsplit,
         _ptr(scratch), _ptr(sinks), cross, 1 if out.dtype == torch.float32 else 0, _stream()))
 
 

@@ -234,7 +234,7 @@ class AttentionMixer(Mixer):
         ``prepare`` when the engine runs it, so that the index arrays travel with the step's metadata)."""
         window = self.kernel_window()
         # the tensor-core kernels take values as wide as the keys (sinks and values in the key rows included)
-        plain = self.v_head_dim == self.head_dim and not self.softcap
+        plain = self.v_head_dim == self.head_dim
         cross = self.value_cross
         key = ("attention_plan", self.num_heads, self.num_kv_heads, self.head_dim, window, dtype, plain, cross)
         plan = ctx.memo.get(key)
@@ -342,7 +342,7 @@ class AttentionMixer(Mixer):
             ops.paged_decode_mma(q, cache.k, v_plane, out, tile_span, tile_q0, ntiles, ctx.span_row, ctx.span_pos,
                                  ctx.block_tables[g], ctx.max_pages, ctx.page_size, self.num_heads,
                                  self.num_kv_heads, self.head_dim, window, self.scale, nsplit, scratch, sinks=self.sinks,
-                                 cross=self.value_cross)
+                                 cross=self.value_cross, softcap=self.softcap or 0.0)
         elif plan[0] == "decode_simt":
             self._simt(q, cache, out, plan[1], common, 1, plan[2])
         else:
@@ -350,13 +350,13 @@ class AttentionMixer(Mixer):
             if items is not None:
                 tile_span, tile_q0, ntiles, cut = items
                 ops.paged_attention_tcgen05(q, cache.k, v_plane, out, tile_span, tile_q0, ntiles, *common, cut=cut,
-                                            sinks=self.sinks, cross=self.value_cross)
+                                            sinks=self.sinks, cross=self.value_cross, softcap=self.softcap or 0.0)
             if decode is not None:
                 (tile_span, tile_q0, ntiles), nsplit = decode
                 ops.paged_decode_mma(q, cache.k, v_plane, out, tile_span, tile_q0, ntiles, ctx.span_row, ctx.span_pos,
                                      ctx.block_tables[g], ctx.max_pages, ctx.page_size, self.num_heads,
                                      self.num_kv_heads, self.head_dim, window, self.scale, nsplit, None, sinks=self.sinks,
-                                     cross=self.value_cross)
+                                     cross=self.value_cross, softcap=self.softcap or 0.0)
             for tiles, bq, nsplit in simt:
                 self._simt(q, cache, out, tiles, common, bq, nsplit)
 
