@@ -36,6 +36,11 @@ __device__ __forceinline__ float silu_fast(float x) { return __fdividef(x, 1.0f 
 template <bool FAST>
 __device__ __forceinline__ float glu_pair(const LlbGluArgs& glu, float g, float u) {
     if (glu.kind == LLB_GLU_SILU) return (FAST ? silu_fast(g) : llb_silu(g)) * u;
+    if (FAST && glu.kind == LLB_GLU_CLAMPED_SWISH) {          // the clamped gate with the fast exponential and division
+        g = fminf(g, glu.limit);
+        u = fminf(fmaxf(u, -glu.limit), glu.limit);
+        return __fdividef(g, 1.0f + __expf(-glu.alpha * g)) * (u + glu.up_shift);
+    }
     return llb_glu(g, u, glu.kind, glu.alpha, glu.limit, glu.up_shift);
 }
 

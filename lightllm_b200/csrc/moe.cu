@@ -18,7 +18,7 @@ namespace {
 constexpr int MOE_MAX_EXPERTS = 512;
 
 template <typename TX>
-__global__ void __launch_bounds__(256) moe_route_kernel(const TX* __restrict__ x, const float* __restrict__ w,
+__global__ void __launch_bounds__(512) moe_route_kernel(const TX* __restrict__ x, const float* __restrict__ w,
                                                         const float* __restrict__ correction, int T, int D, int E, int top,
                                                         int softmax, int renorm, float scale, int* __restrict__ ids,
                                                         float* __restrict__ weights, float* __restrict__ dense, int real,
@@ -139,15 +139,24 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const TX* __restrict__ x
 }
 
 // act[t, e * F + j] *= dense[t, e]; exactly zero where the expert was not chosen, whatever the activation holds.
+// One block per (token, expert): the weight is read once, the F activations in 16-byte pieces where they are aligned.
 template <typename TA>
-__global__ void moe_scale_kernel(TA* __restrict__ act, const float* __restrict__ dense, long long n, int E, int F) {
-    const long long stride = (long long)gridDim.x * blockDim.x;
-    const long long row = (long long)E * F;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
-        const long long t = i / row;
-        const int e = (int)((i - t * row) / F);
-        const float wgt = dense[t * E + e];
-        act[i] = wgt == 0.0f ? llb_from_float<TA>(0.0f) : llb_from_float<TA>(llb_to_float(act[i]) * wgt);
+__global__ void __launch_bounds__(128) moe_scale_kernel(TA* __restrict__ act, const float* __restrict__ dense, int F) {
+    const float wgt = dense[blockIdx.x];
+    TA* a = act + (size_t)blockIdx.x * F;
+    constexpr int V = 16 / sizeof(TA);
+    if (F % V == 0 && (uintptr_t)act % 16 == 0) {
+        uint4* a4 = reinterpret_cast<uint4*>(a);
+        for (int i = threadIdx.x; i < F / V; i += blockDim.x) {
+            uint4 raw = a4[i];
+            TA* e = reinterpret_cast<TA*>(&raw);
+#pragma unroll
+            for (int j = 0; j < V; ++j) e[j] = wgt == 0.0f ? llb_from_float<TA>(0.0f) : llb_from_float<TA>(llb_to_float(e[j]) * wgt);
+            a4[i] = raw;
+        }
+    } else {
+        for (int i = threadIdx.x; i < F; i += blockDim.x)
+            a[i] = wgt == 0.0f ? llb_from_float<TA>(0.0f) : llb_from_float<TA>(llb_to_float(a[i]) * wgt);
     }
 }
 
@@ -397,9 +406,9 @@ LLB_EXPORT int llb_moe_route_ex(const void* x, int x_dtype, const float* w, cons
                 "moe_route: %d experts in %d groups of which %d are kept", E, groups, keep);
     LLB_REQUIRE(groups <= 1 || (long long)keep * (E / groups) >= top, "moe_route: the kept groups hold fewer than %d experts", top);
     LLB_REQUIRE(n_gate >= 0 && (n_gate == 0 || gate_out != nullptr), "moe_route: gate rows without an output");
-    // a block a token; as many warps as there are rows to walk side by side, at most eight
+    // a block a token; as many warps as there are rows to walk side by side, at most sixteen
     const int rows = E + n_gate;
-    const int warps = rows < 8 ? rows : 8;
+    const int warps = rows < 16 ? rows : 16;
     const size_t smem = (size_t)(((D + 3) & ~3) + 2 * E + (groups > 1 ? groups : 0)) * sizeof(float);
     LLB_REQUIRE(smem <= 48 * 1024, "moe_route: rows of %d numbers do not fit in shared memory", D);
     const unsigned blocks = (unsigned)T;
@@ -427,10 +436,10 @@ LLB_EXPORT int llb_moe_route(const void* x, int x_dtype, const float* w, const f
 LLB_EXPORT int llb_moe_scale(void* act, int dtype, const float* dense, int T, int E, int F, cudaStream_t stream) {
     if (T == 0) return 0;
     LLB_REQUIRE(T > 0 && E > 0 && F > 0 && act && dense, "moe_scale: bad arguments");
-    const long long n = (long long)T * E * F;
-    const int blocks = (int)((n + 255) / 256 < 2368 ? (n + 255) / 256 : 2368);
-    if (dtype == LLB_F32) moe_scale_kernel<float><<<blocks, 256, 0, stream>>>((float*)act, dense, n, E, F);
-    else if (dtype == LLB_BF16) moe_scale_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((__nv_bfloat16*)act, dense, n, E, F);
+    LLB_REQUIRE((long long)T * E < (1ll << 31), "moe_scale: too many rows");
+    const unsigned blocks = (unsigned)((long long)T * E);
+    if (dtype == LLB_F32) moe_scale_kernel<float><<<blocks, 128, 0, stream>>>((float*)act, dense, F);
+    else if (dtype == LLB_BF16) moe_scale_kernel<__nv_bfloat16><<<blocks, 128, 0, stream>>>((__nv_bfloat16*)act, dense, F);
     else return llb_fail("moe_scale: unknown dtype %d", dtype);
     return llb_check_launch("moe_scale");
 }
