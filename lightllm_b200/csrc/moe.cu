@@ -406,9 +406,11 @@ LLB_EXPORT int llb_moe_route_ex(const void* x, int x_dtype, const float* w, cons
                 "moe_route: %d experts in %d groups of which %d are kept", E, groups, keep);
     LLB_REQUIRE(groups <= 1 || (long long)keep * (E / groups) >= top, "moe_route: the kept groups hold fewer than %d experts", top);
     LLB_REQUIRE(n_gate >= 0 && (n_gate == 0 || gate_out != nullptr), "moe_route: gate rows without an output");
-    // a block a token; as many warps as there are rows to walk side by side, at most sixteen
+    // a block a token; as many warps as there are rows to walk side by side: at most sixteen in a step of few tokens (one
+    // pass over the rows), eight otherwise (the choice is one warp's work, and idle warps keep other tokens' blocks out)
     const int rows = E + n_gate;
-    const int warps = rows < 16 ? rows : 16;
+    const int most = T < 64 ? 16 : 8;
+    const int warps = rows < most ? rows : most;
     const size_t smem = (size_t)(((D + 3) & ~3) + 2 * E + (groups > 1 ? groups : 0)) * sizeof(float);
     LLB_REQUIRE(smem <= 48 * 1024, "moe_route: rows of %d numbers do not fit in shared memory", D);
     const unsigned blocks = (unsigned)T;

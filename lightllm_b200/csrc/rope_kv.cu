@@ -262,6 +262,7 @@ __global__ void __launch_bounds__(256) head_prepare_kernel(
     int v_mode, int v_width, const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w, float eps,
     const int* __restrict__ positions, const float* __restrict__ inv_freq, int rotary_dim, int interleaved,
     const int* __restrict__ slot_mapping, T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache) {
+    extern __shared__ float2 cs[];          // (cos, sin) of the token's angles, one a pair: every head turns by the same
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31;
     const int warps = (blockDim.x >> 5) * gridDim.y;
@@ -271,6 +272,11 @@ __global__ void __launch_bounds__(256) head_prepare_kernel(
     const int slot = slot_mapping ? slot_mapping[t] : -1;
     const int half = rotary_dim / 2;
     const int per_head = hd - half;
+    for (int j = threadIdx.x; j < half; j += blockDim.x) {
+        const float angle = (float)pos * inv_freq[j];
+        cs[j] = make_float2(cosf(angle), sinf(angle));
+    }
+    __syncthreads();
     for (int head = warp; head < Hq + Hk; head += warps) {
         const bool is_q = head < Hq;
         const int h = is_q ? head : head - Hq;
@@ -311,8 +317,7 @@ __global__ void __launch_bounds__(256) head_prepare_kernel(
                     a = a * inv * w[ia];
                     b = b * inv * w[ib];
                 }
-                const float angle = (float)pos * inv_freq[j];
-                const float c = cosf(angle), sn = sinf(angle);
+                const float c = cs[j].x, sn = cs[j].y;
                 dst[ia] = llb_from_float<T>(a * c - b * sn);
                 dst[ib] = llb_from_float<T>(b * c + a * sn);
             } else {
@@ -355,12 +360,13 @@ LLB_EXPORT int llb_head_prepare(const void* src, int dtype, long long row_stride
     int share = T >= 128 ? 1 : (heads + 7) / 8;
     if (share > 8) share = 8;
     const dim3 grid(T, share < 1 ? 1 : share);
+    const size_t smem = (size_t)(rotary_dim / 2) * sizeof(float2);
     if (dtype == LLB_F32)
-        head_prepare_kernel<float><<<grid, 256, 0, stream>>>(
+        head_prepare_kernel<float><<<grid, 256, smem, stream>>>(
             (const float*)src, row_stride, q_off, k_off, v_off, Hq, Hk, hd, q_maps, v_mode, v_width, q_norm_w, k_norm_w, eps,
             positions, inv_freq, rotary_dim, interleaved, slot_mapping, (float*)q_out, (float*)k_cache, (float*)v_cache);
     else if (dtype == LLB_BF16)
-        head_prepare_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(
+        head_prepare_kernel<__nv_bfloat16><<<grid, 256, smem, stream>>>(
             (const __nv_bfloat16*)src, row_stride, q_off, k_off, v_off, Hq, Hk, hd, q_maps, v_mode, v_width, q_norm_w,
             k_norm_w, eps, positions, inv_freq, rotary_dim, interleaved, slot_mapping, (__nv_bfloat16*)q_out,
             (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache);
