@@ -69,7 +69,7 @@ class FediraxConfig(ModelConfig):
             raise ConfigError(f"{where}: 'mixer' must be an object")
         r = ConfigReader(raw, where)
         out: Dict[str, Any] = {"heads": r.integer("heads"), "kv_heads": r.integer("kv_heads"), "dim": r.integer("dim"),
-                               "vdim": r.integer("vdim"), "scale": r.real("scale"), "window": None, "rot": None}
+                               "vdim": r.integer("vdim", None), "scale": r.real("scale"), "window": None, "rot": None}
         if out["heads"] % out["kv_heads"]:
             raise ConfigError(f"{where}: 'heads' {out['heads']} is not a multiple of 'kv_heads' {out['kv_heads']}")
         mask = _object(raw, "mask", where, required=False)
@@ -84,10 +84,11 @@ class FediraxConfig(ModelConfig):
             if dims:
                 out["rot"] = {"dims": dims, "base": rr.real("base")}
         if kind == "attention":
-            if out["vdim"] != out["dim"]:
-                raise ConfigError(f"{where}: the values are the keys, so 'vdim' {out['vdim']} must equal 'dim' {out['dim']}")
+            out["vdim"] = out["dim"]          # the values are the keys: their width is the keys'
             out["softcap"] = r.real("softcap") if raw.get("softcap") is not None else None
         else:
+            if out["vdim"] is None:
+                raise ConfigError(f"{where}: required key 'vdim' is missing")
             out["diff"] = r.real("diff", positive=False)
             out["kv_from"] = r.integer("kv_from", None, minimum=0)
         return out

@@ -88,8 +88,17 @@ FED_D = {"architecture": "Fedirax", "vocab": 211, "width": 50, "embedding": {"sc
     _moe(_diff(6, 1, 6, 10, 8, 2, 0.6, kv_from=1), 16, 7, 2, 3.0, groups=(7, 3)),
     _moe(_diff(6, 1, 6, 10, 48, 2, 0.15, kv_from=1), None, 0, 0, 0),
 ]}
-CONFIGS = {"A": FED_A, "B": FED_B, "C": FED_C, "D": FED_D}
-PAGE_SIZE = {"A": 16, "B": 16, "C": 8, "D": 16}
+# E: thirty-two query rows a kv head (more than the tensor-core decode kernel takes: single tokens fall back to the
+# CUDA-core kernel while portions stay on the tensor cores), as many kv heads as heads, a window longer than any
+# sequence of the tests, a feed-forward of identity experts alone, experts whose width is a multiple of nothing.
+FED_E = {"architecture": "Fedirax", "vocab": 150, "width": 64, "embedding": {"scale": 6.0}, "norm": {"eps": 1e-6}, "layers": [
+    _moe(_diff(16, 1, 12, 20, 50, 4, 0.2), 16, 0, 2, 1.2, identity=3),
+    _moe(_sink(4, 4, 16, 5000, 8, 50.0), 18, 5, 2, 1.0, limit=2.0, identity=1, groups=(3, 2), shared=(10, 1.0)),
+    _moe(_diff(16, 1, 32, 64, 100, 32, 0.3, base=1000.0), 24, 3, 2, 1.5, shared=(8, 4.0)),
+    _moe(_diff(2, 2, 16, 32, 64, 16, 0.5), None, 0, 0, 0),
+]}
+CONFIGS = {"A": FED_A, "B": FED_B, "C": FED_C, "D": FED_D, "E": FED_E}
+PAGE_SIZE = {"A": 16, "B": 16, "C": 8, "D": 16, "E": 16}
 
 
 def config(name):

@@ -44,7 +44,7 @@ def _broken(edit):
     (lambda c: c["layers"][0]["mixer"].pop("heads"), "heads"),
     (lambda c: c["layers"][0]["mixer"].update(kv_heads=3), "kv_heads"),
     (lambda c: c["layers"][0]["mixer"]["rot"].update(dims=7), "dims"),
-    (lambda c: c["layers"][1]["mixer"].update(vdim=10), "vdim"),
+    (lambda c: c["layers"][0]["mixer"].pop("vdim"), "vdim"),
     (lambda c: c["layers"][2]["mixer"].update(kv_from=3), "kv_from"),
     (lambda c: c["layers"][2]["mixer"].update(kv_from=1), "kv_from"),
     (lambda c: c["layers"][2]["mixer"].update(dim=12), "dim"),

@@ -238,7 +238,7 @@ def error(got, plain, dtype) -> float:
 
 
 LENGTHS = {"A": [1, 2, 17, 33, 70, 150, 64, 49], "B": [3, 40, 131, 330, 129, 520, 64, 257], "C": [1, 5, 40, 90, 33, 64, 17, 200],
-           "D": [1, 3, 20, 45, 16, 70, 33, 97]}
+           "D": [1, 3, 20, 45, 16, 70, 33, 97], "E": [2, 1, 35, 130, 64, 18, 210, 51]}
 
 
 def build_trace(name, cfg, seed=11):
@@ -345,7 +345,7 @@ def test_heavy_sinks_and_a_far_key_that_stands_out(tmp_path, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "C", "D", "E"])
 def test_prefill_equals_token_by_token_and_long_decoding(tmp_path, name, dtype):
     """A whole prompt in one step against the same tokens one by one from the first (300 single steps: every window
     passes, pages fill up and are given back behind the windows)."""
@@ -363,7 +363,7 @@ def test_prefill_equals_token_by_token_and_long_decoding(tmp_path, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_a_batch_of_unequal_requests_equals_each_alone_and_slots_are_used_again(tmp_path, name, dtype):
     d, cfg, w = make_model(tmp_path, name, dtype, seed=6)
     rng = random.Random(7)

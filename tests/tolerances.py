@@ -76,6 +76,7 @@ FEDIRAX_BF16_WORST_REL = {"A": 0.0085,         # replay 0.0073, batch 0.0071, to
                           "B": 0.0030,         # replay 0.0026, batch 0.0024
                           "C": 0.025,          # replay 0.0216, batch 0.0121 (width 32, one head of 8)
                           "D": 0.0048,         # batch 0.0042, token by token 0.0042, replay 0.0037
+                          "E": 0.0032,         # replay 0.0028, batch 0.0027, token by token 0.0027
                           "A sharp": 0.022, "B sharp": 0.0054, "D sharp": 0.0145,          # 0.0188, 0.0047, 0.0125
                           "A sinks": 0.0080, "B sinks": 0.0033}                            # 0.0070, 0.0028
 
