@@ -186,6 +186,107 @@ def test_experts_with_identity_and_shared_expert(dtype, T, E, ident, top, groups
     ops.check_async_errors(DEV)
 
 
+def paged(k, pages, page, dtype):
+    n = k.shape[0]
+    cache = torch.full((64 * page, *k.shape[1:]), float("nan"), dtype=DT[dtype])
+    cache[pages[torch.arange(n) // page].long() * page + torch.arange(n) % page] = k
+    return dev(cache)
+
+
+def capped_case(dtype, H, G, hd, window, cap, n, page, seed):
+    """Keys, values and a plain result in which the cap matters (raw scores reach three times the cap), the sinks weigh
+    as much as a key at the cap, and the last row's first head matches the key just inside its window and the key just
+    outside it alike: the second must not be seen."""
+    torch.manual_seed(seed)
+    k, v = torch.randn(n, G, hd).to(DT[dtype]), torch.randn(n, G, hd).to(DT[dtype])
+    pages = torch.randperm(64)[: -(-n // page)].to(torch.int32)
+    sinks = torch.randn(H) * 0.5 + cap          # as heavy as a key at the cap
+    scale = 3.0 * cap / hd          # q = 1 * k gives a raw score near 3 cap
+    return k, v, pages, sinks, scale
+
+
+def capped_plain(q, k, v, start, scale, window, cap, sinks):
+    n = start + q.shape[0]
+    pad = torch.zeros(start, *q.shape[1:], dtype=torch.float64)
+    full = P.windowed_attention(torch.cat([pad, q.double()]), k[:n].double(), v[:n].double(), scale, window, cap, sinks.double())
+    return full[start:]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,G,hd,window", [(4, 2, 12, 23), (3, 3, 20, 9), (6, 1, 18, 40), (2, 2, 64, 50), (5, 5, 34, 16)])
+def test_cuda_core_attention_with_a_cap_sinks_and_a_window(dtype, H, G, hd, window):
+    cap, page, n = 4.0, 8, 170
+    k, v, pages, sinks, scale = capped_case(dtype, H, G, hd, window, cap, n, page, H * hd)
+    kc, vc, bt = paged(k, pages, page, dtype), paged(v, pages, page, dtype), dev(pages.view(1, -1))
+    from lightllm_b200.parts.sink_attention import KeyValuedAttentionMixer
+    part = KeyValuedAttentionMixer("m", 32, H, G, hd, window=window, scale=scale, softcap=cap)
+    for start, rows, bq, nsplit in ((120, 50, part.tile_height(), 1), (120, 50, 1, 3), (0, 30, part.tile_height(), 1),
+                                    (n - 1, 1, 1, 1), (n - 1, 1, 1, 4)):
+        q = torch.randn(rows, H, hd).to(DT[dtype])
+        last = start + rows - 1
+        if last - window >= 0:
+            q[-1, 0] = k[last - window + 1, 0] + k[last - window, 0]          # the first key the window still holds, and the one before it
+        want = capped_plain(q, k, v, start, scale, window, cap, sinks)
+        out = torch.full((rows, H * hd), float("nan"), dtype=DT[dtype], device=DEV)
+        tq0 = list(range(0, rows, bq))
+        scratch = torch.empty(ops.attention_scratch_floats(len(tq0), H, hd, bq, nsplit), device=DEV) if nsplit > 1 else None
+        ops.paged_attention_simt(dev(q).view(rows, H * hd), kc, vc, out, i32([0] * len(tq0)), i32(tq0), len(tq0), i32([0]),
+                                 i32([rows]), i32([start]), bt, bt.shape[1], page, H, G, hd, window, scale, bq, nsplit, scratch,
+                                 sinks=dev(sinks), softcap=cap)
+        close(out.view(rows, H, hd), want, dtype, f"start {start}, {rows} rows, bq {bq}, {nsplit} pieces",
+              rel=None if dtype == "float32" else 1.5e-2)
+        # what the mechanisms are worth here: without the cap, without the sinks, with a window one longer
+        if last - window < 0:
+            continue
+        for other in (capped_plain(q, k, v, start, scale, window, None, sinks),
+                      capped_plain(q, k, v, start, scale, window, cap, torch.full_like(sinks, -50.0)),
+                      capped_plain(q, k, v, start, scale, window + 1, cap, sinks)):
+            assert float((other[-1, 0] - want[-1, 0]).abs().max()) > 0.05 * float(want[-1, 0].abs().max())          # the made row
+
+
+@pytest.mark.parametrize("H,G,hd,window", [(4, 2, 64, 150), (4, 1, 128, 200), (2, 2, 64, 16), (16, 1, 64, 129), (2, 2, 128, 300)])
+def test_tensor_core_attention_with_a_cap_sinks_and_a_window(H, G, hd, window):
+    """The capped instantiation of the tcgen05 kernel (portions, whole key ranges and ranges cut into pieces) and the
+    capped branch of the decode kernel (pieces merged in a cluster and through scratch), against the plain attention."""
+    cap, page, n = 6.0, 16, 700
+    k, v, pages, sinks, scale = capped_case("bfloat16", H, G, hd, window, cap, n, page, H + hd)
+    kc, vc, bt = paged(k, pages, page, "bfloat16"), paged(v, pages, page, "bfloat16"), dev(pages.view(1, -1))
+    from lightllm_b200.engine.batch import Span, StepContext
+    for start, rows, pieces in ((0, 300, None), (380, 320, 2), (690, 10, None), (250, 135, 1), (3, 2, None)):
+        q = torch.randn(rows, H, hd).to(torch.bfloat16)
+        last = start + rows - 1
+        if last - window >= 0:
+            q[-1, 0] = k[last - window + 1, 0] + k[last - window, 0]
+        out = torch.full((rows, H * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+        ctx = StepContext()
+        ctx.spans, ctx.device = [Span("a", 0, start, rows, 0)], DEV
+        ctx.iota, ctx.zeros = i32([0]), i32([0])
+        ts, tq, nt, cut = ctx.attention_items(1, window, pieces, H, 296)
+        ops.paged_attention_tcgen05(dev(q).view(rows, H * hd), kc, vc, out, ts, tq, nt, i32([0]), i32([rows]), i32([start]),
+                                    bt, bt.shape[1], page, H, G, hd, window, scale, cut=cut, sinks=dev(sinks), softcap=cap)
+        ops.check_async_errors(DEV)
+        want = capped_plain(q, k, v, start, scale, window, cap, sinks)
+        close(out.view(rows, H, hd), want, "bfloat16", f"tcgen05, start {start}, {rows} rows, pieces of {pieces}", rel=1.5e-2)
+        if last - window >= 0:
+            longer = capped_plain(q, k, v, start, scale, window + 1, cap, sinks)
+            assert float((longer[-1, 0] - want[-1, 0]).abs().max()) > 0.05 * float(want[-1, 0].abs().max())
+    if not ops.paged_decode_mma_supports(H, G, hd):
+        return
+    for pos in (n - 1, 130, 0):
+        for nsplit in (1, 4, 20):
+            q = torch.randn(1, H, hd).to(torch.bfloat16)
+            if pos - window >= 0:
+                q[0, H - 1] = k[pos - window + 1, G - 1] + k[pos - window, G - 1]
+            out = torch.full((1, H * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+            scratch = None
+            if nsplit > ops.decode_mma_cluster_splits():
+                scratch = torch.empty(ops.attention_scratch_floats(1, H, hd, 1, nsplit), device=DEV)
+            ops.paged_decode_mma(dev(q).view(1, H * hd), kc, vc, out, i32([0]), i32([0]), 1, i32([0]), i32([pos]), bt,
+                                 bt.shape[1], page, H, G, hd, window, scale, nsplit, scratch, sinks=dev(sinks), softcap=cap)
+            close(out.view(1, H, hd), capped_plain(q, k, v, pos, scale, window, cap, sinks), "bfloat16",
+                  f"decode at {pos}, {nsplit} pieces", rel=1.5e-2)
+
+
 # ---------------------------------------------------------------------------------------------------------------------
 # the model through the engine
 # ---------------------------------------------------------------------------------------------------------------------
