@@ -295,6 +295,64 @@ def main(argv=None) -> int:
                                                 btp.shape[1], page, Hq, Hkv, hd, -chunk_c, 1 / math.sqrt(hd), cut=cut),
             (2 * T * Hq * hd + 2 * T * Hkv * hd) * 2, 2 * 2 * Hq * hd * keys_seen)
 
+    # ---- differential and keys-as-values attention, grouped routing (windows of 1,024) ---------------------------------
+    window_w = 1024
+    if ops.attention_tcgen05_supports(hd, page) and T > 128:
+        from lightllm_b200.engine.batch import cut_attention_rows, first_visible
+        from lightllm_b200.parts import linear as L
+        import numpy as np
+        sinks_w = rn(Hq)
+        rows_w = [(0, q0, -(-(min(q0 + 128, T) - (first_visible(q0, window_w) // 128) * 128) // 128)) for q0 in range(0, T, 128)]
+        for heads_w, cap_w, label in ((Hq, 30.0, "capped_sinks"), (2 * Hq, 0.0, "two_maps_a_head")):
+            items, merges, parts = cut_attention_rows(rows_w, None, heads_w, (2 if hd <= 64 else 1) * L.num_sms(dev))
+            arr = torch.from_numpy(np.asarray([t[1:] for t in items], dtype=np.int32).T.copy()).to(dev)
+            m = torch.from_numpy(np.asarray(merges, dtype=np.int32).reshape(-1, 4).T.copy()).to(dev)
+            cut = (arr[2], arr[3], arr[4], parts, m[0], m[1], m[2], m[3], len(merges)) if merges else (arr[2], arr[3], arr[4], 0, None, None, None, None, 0)
+            keys_seen = sum(p - first_visible(p, window_w) + 1 for p in range(T))
+            qw = rn(T, heads_w * hd, dtype=torch.bfloat16)
+            ow = torch.empty((T, heads_w * hd), dtype=torch.float32 if cap_w == 0.0 else torch.bfloat16, device=dev)
+            ts_w, tq_w = arr[0].contiguous(), arr[1].contiguous()
+            run(f"paged_attention_tcgen05_window_1024_{label}",
+                lambda: ops.paged_attention_tcgen05(qw, kcp, vcp, ow, ts_w, tq_w, len(items), sr, sl, sp, btp, btp.shape[1], page,
+                                                    heads_w, Hkv, hd, window_w, 1 / math.sqrt(hd), cut=cut,
+                                                    sinks=sinks_w if cap_w else None, softcap=cap_w),
+                (2 * T * heads_w * hd + 2 * T * Hkv * hd) * 2, 2 * 2 * heads_w * hd * keys_seen)
+    if hd % 2 == 0:
+        # differential: 2 Hq query maps and 2 Hkv key maps of hd / 2, values of hd, q and k normed map by map
+        dm = hd // 2
+        Nd = 2 * Hq * dm + 2 * Hkv * dm + Hkv * hd
+        fused_d = rn(T, Nd, dtype=torch.bfloat16)
+        qd_out = torch.empty((T, 2 * Hq * hd), dtype=torch.bfloat16, device=dev)
+        nw = torch.ones(dm, device=dev)
+        inv_d = (1.0 / 250000.0 ** (torch.arange(0, dm, 2, dtype=torch.float64) / dm)).float().to(dev)
+        run("head_prepare_two_maps_norm_rope_cache",
+            lambda: ops.head_prepare(fused_d, 0, 2 * Hq * dm, 2 * Hq, 2 * Hkv, dm, positions, positions, qd_out, kc, vc, q_maps=2,
+                                     values="columns", v_off=2 * (Hq + Hkv) * dm, v_width=Hkv * hd, q_norm_w=nw, k_norm_w=nw,
+                                     eps=1e-6, inv_freq=inv_d, rotary_dim=dm, interleaved=True),
+            (T * Nd + T * 2 * Hq * hd + 2 * T * Hkv * hd) * 2)
+        Nk = (Hq + Hkv) * hd + 8
+        fused_k = rn(T, Nk, dtype=torch.bfloat16)
+        run("head_prepare_keys_as_values_rope_cache",
+            lambda: ops.head_prepare(fused_k, 0, Hq * hd, Hq, Hkv, hd, positions, positions, q_out, kc, vc, values="keys",
+                                     inv_freq=inv_freq, rotary_dim=hd, interleaved=True),
+            (T * (Hq + Hkv) * hd + T * Hq * hd + 2 * T * Hkv * hd) * 2)
+        maps_d = rn(T, 2 * Hq * hd)
+        heads_d = torch.empty((T, Hq * hd), dtype=torch.bfloat16, device=dev)
+        run("diff_combine", lambda: ops.diff_combine(maps_d, heads_d, Hq, hd, 0.7, 1e-6, 0.7), T * Hq * hd * (8 + 2))
+    Er, Ei = 8, 2
+    w_router_g = rn(Er + Ei + 1, D, s=D ** -0.5)
+    corr_g = rn(Er + Ei, s=0.1)
+    g_ids = torch.empty((T, 2), dtype=torch.int32, device=dev)
+    g_w, g_dense = torch.empty((T, 2), device=dev), torch.empty((T, Er), device=dev)
+    g_idw, g_gate = torch.empty(T, device=dev), torch.empty((T, 1), device=dev)
+    x_g = rn(T, D, dtype=torch.bfloat16)
+    run("moe_route_groups_identity_gate",
+        lambda: ops.moe_route(x_g, w_router_g, corr_g, 2, 2.0, g_ids, g_w, g_dense, softmax=True, renormalize=True, renorm_eps=1e-20,
+                              real=Er, groups=2, keep=1, identity_weight=g_idw, gate_rows=1, gate_out=g_gate),
+        T * D * 2 + T * (Er + 8) * 4, 2 * T * D * (Er + Ei + 1))
+    act_s = rn(T, I // 4, dtype=torch.bfloat16)
+    run("moe_scale_one_gate_a_token", lambda: ops.moe_scale(act_s, g_gate, 1, I // 4), 2 * T * (I // 4) * 2)
+
     # ---- what a decode step of B requests over C keys runs --------------------------------------------------------------
     pages_per = -(-(C + 1) // page)
     kcd = rn(B * pages_per * page, Hkv, hd, dtype=torch.bfloat16)
@@ -308,6 +366,11 @@ def main(argv=None) -> int:
         nsplit = max(1, min(8, ops.decode_mma_resident(hd) * 148 // (B * Hkv), -(-(C + 1) // 128)))
         run("paged_decode_mma", lambda: ops.paged_decode_mma(qd, kcd, vcd, od, rows, zero, B, rows, pos, btd, pages_per, page, Hq,
                                                              Hkv, hd, 0, 1 / math.sqrt(hd), nsplit, None), kv_bytes)
+        sinks_d = rn(Hq)
+        run("paged_decode_mma_window_1024_capped_sinks",
+            lambda: ops.paged_decode_mma(qd, kcd, vcd, od, rows, zero, B, rows, pos, btd, pages_per, page, Hq, Hkv, hd, 1024,
+                                         1 / math.sqrt(hd), nsplit, None, sinks=sinks_d, softcap=30.0),
+            B * min(C + 1, 1024) * Hkv * hd * 2 * 2)
         big = 24           # more pieces than a cluster merges: the pieces meet in scratch and a second kernel merges them
         scratch = torch.empty(ops.attention_scratch_floats(B, Hq, hd, 1, big), device=dev)
         run("paged_decode_mma_and_merge", lambda: ops.paged_decode_mma(qd, kcd, vcd, od, rows, zero, B, rows, pos, btd, pages_per,
