@@ -389,7 +389,7 @@ def fedirax_config(base: dict, layers: int, kinds=("attention_2", "attention"), 
     """A Fedirax model with the width, head count, head size and vocabulary of a Qwen2 configuration.  Its layers cycle
     through ``kinds``: differential layers with the base's heads, two maps of half the base's head size each (so a key
     row and a value row are as wide as the base's) and, from the third on, keys and values read from the first such
-    layer (``share``); keys-as-values layers with the base's heads, a cap of 30 and a sink.  Windows of 1,024, full
+    layer (``share``); keys-as-values layers with the base's heads, a cap of 50 and a sink.  Windows of 1,024, full
     rotation.  ``experts`` experts of which ``top`` are chosen, each as wide as the dense feed-forward divided by
     ``top``, two identity experts beside them, two groups of which one is kept, and a shared expert of a quarter of the
     dense width."""
@@ -397,12 +397,12 @@ def fedirax_config(base: dict, layers: int, kinds=("attention_2", "attention"), 
     hd = base.get("head_dim", D // H)
     mixers = {
         "attention": {"heads": H, "kv_heads": G, "dim": hd, "vdim": hd, "mask": {"size": 1024}, "scale": hd ** -0.5,
-                      "softcap": 30.0, "rot": {"dims": hd, "base": 500000.0}},
+                      "softcap": 50.0, "rot": {"dims": hd, "base": 1000000.0}},
         "attention_2": {"heads": H, "kv_heads": G, "dim": hd // 2, "vdim": hd, "mask": {"size": 1024},
-                        "scale": (hd // 2) ** -0.5, "diff": 0.3, "rot": {"dims": hd // 2, "base": 250000.0}},
+                        "scale": (hd // 2) ** -0.5, "diff": 0.25, "rot": {"dims": hd // 2, "base": 100000.0}},
     }
     mlp = {"kind": "moe", "expert": {"ff": base["intermediate_size"] // top, "limit": 7.0},
-           "router": {"experts": experts, "top": top, "scale": 2.0, "identity": 2, "groups": {"count": 2, "keep": 1}},
+           "router": {"experts": experts, "top": top, "scale": 2.5, "identity": 2, "groups": {"count": 2, "keep": 1}},
            "shared": {"ff": base["intermediate_size"] // 4, "limit": 7.0}}
     out, first = [], None
     for i in range(layers):
@@ -414,8 +414,8 @@ def fedirax_config(base: dict, layers: int, kinds=("attention_2", "attention"), 
             elif share and sum(l["type"] == kind for l in out) >= 2:
                 mixer["kv_from"] = first
         out.append({"type": kind, "mixer": mixer, "mlp": mlp})
-    return {"architecture": "Fedirax", "vocab": base["vocab_size"], "width": D, "embedding": {"scale": 3.0},
-            "norm": {"eps": 1e-6}, "layers": out}
+    return {"architecture": "Fedirax", "vocab": base["vocab_size"], "width": D, "embedding": {"scale": 4.0},
+            "norm": {"eps": 1e-5}, "layers": out}
 
 
 def run_design(name: str, sizes: str, layers: int, steps: int, warmup: int, only=None) -> int:

@@ -303,7 +303,7 @@ def main(argv=None) -> int:
         import numpy as np
         sinks_w = rn(Hq)
         rows_w = [(0, q0, -(-(min(q0 + 128, T) - (first_visible(q0, window_w) // 128) * 128) // 128)) for q0 in range(0, T, 128)]
-        for heads_w, cap_w, label in ((Hq, 30.0, "capped_sinks"), (2 * Hq, 0.0, "two_maps_a_head")):
+        for heads_w, cap_w, label in ((Hq, 50.0, "capped_sinks"), (2 * Hq, 0.0, "two_maps_a_head")):
             items, merges, parts = cut_attention_rows(rows_w, None, heads_w, (2 if hd <= 64 else 1) * L.num_sms(dev))
             arr = torch.from_numpy(np.asarray([t[1:] for t in items], dtype=np.int32).T.copy()).to(dev)
             m = torch.from_numpy(np.asarray(merges, dtype=np.int32).reshape(-1, 4).T.copy()).to(dev)
@@ -324,7 +324,7 @@ def main(argv=None) -> int:
         fused_d = rn(T, Nd, dtype=torch.bfloat16)
         qd_out = torch.empty((T, 2 * Hq * hd), dtype=torch.bfloat16, device=dev)
         nw = torch.ones(dm, device=dev)
-        inv_d = (1.0 / 250000.0 ** (torch.arange(0, dm, 2, dtype=torch.float64) / dm)).float().to(dev)
+        inv_d = (1.0 / 100000.0 ** (torch.arange(0, dm, 2, dtype=torch.float64) / dm)).float().to(dev)
         run("head_prepare_two_maps_norm_rope_cache",
             lambda: ops.head_prepare(fused_d, 0, 2 * Hq * dm, 2 * Hq, 2 * Hkv, dm, positions, positions, qd_out, kc, vc, q_maps=2,
                                      values="columns", v_off=2 * (Hq + Hkv) * dm, v_width=Hkv * hd, q_norm_w=nw, k_norm_w=nw,
@@ -369,7 +369,7 @@ def main(argv=None) -> int:
         sinks_d = rn(Hq)
         run("paged_decode_mma_window_1024_capped_sinks",
             lambda: ops.paged_decode_mma(qd, kcd, vcd, od, rows, zero, B, rows, pos, btd, pages_per, page, Hq, Hkv, hd, 1024,
-                                         1 / math.sqrt(hd), nsplit, None, sinks=sinks_d, softcap=30.0),
+                                         1 / math.sqrt(hd), nsplit, None, sinks=sinks_d, softcap=50.0),
             B * min(C + 1, 1024) * Hkv * hd * 2 * 2)
         big = 24           # more pieces than a cluster merges: the pieces meet in scratch and a second kernel merges them
         scratch = torch.empty(ops.attention_scratch_floats(B, Hq, hd, 1, big), device=dev)

@@ -65,8 +65,8 @@ FED_A = {"architecture": "Fedirax", "vocab": 301, "width": 44, "embedding": {"sc
 # and across page borders, a layer that reads its neighbour's cache, eight router outputs in four groups (grouped
 # contractions from 48 rows on).
 FED_B = {"architecture": "Fedirax", "vocab": 517, "width": 128, "embedding": {"scale": 8.0}, "norm": {"eps": 1e-6}, "layers": [
-    _moe(_diff(4, 2, 32, 64, 150, 16, 0.3, base=250000.0), 64, 6, 2, 2.0, identity=2, groups=(4, 2), shared=(64, 1.0)),
-    _moe(_sink(4, 1, 64, 200, 64, 20.0, base=500000.0), 64, 6, 2, 2.0, identity=2, groups=(4, 2), shared=(64, 1.0)),
+    _moe(_diff(4, 2, 32, 64, 150, 16, 0.35, base=100000.0), 64, 6, 2, 1.8, identity=2, groups=(4, 2), shared=(64, 1.0)),
+    _moe(_sink(4, 1, 64, 200, 64, 20.0, base=1000000.0), 64, 6, 2, 1.8, identity=2, groups=(4, 2), shared=(64, 1.0)),
     _moe(_diff(2, 2, 64, 128, 300, 32, 0.1), 32, 8, 3, 1.0, groups=(2, 1)),
     _moe(_diff(2, 2, 64, 128, 130, 32, 0.4, kv_from=2), None, 0, 0, 0),
     _moe(_sink(2, 2, 128, 129, 32, None), 64, 4, 4, 1.5, limit=3.0, shared=(32, 0.5)),
@@ -84,7 +84,7 @@ FED_C = {"architecture": "Fedirax", "vocab": 97, "width": 32, "norm": {"eps": 1e
 # cache with a shorter and a longer window, identity experts that outnumber the experts, rotation of two dimensions.
 FED_D = {"architecture": "Fedirax", "vocab": 211, "width": 50, "embedding": {"scale": 4.0}, "norm": {"eps": 1e-5}, "layers": [
     _moe(_sink(8, 2, 6, 32, 6, 8.0, base=100.0), 24, 2, 2, 1.5, identity=4, groups=(3, 2), shared=(16, 1.5)),
-    _moe(_diff(6, 1, 6, 10, 16, 2, 0.3), 24, 2, 2, 1.5, identity=4, groups=(3, 2)),
+    _moe(_diff(6, 1, 6, 10, 16, 2, 0.45), 24, 2, 2, 1.5, identity=4, groups=(3, 2)),
     _moe(_diff(6, 1, 6, 10, 8, 2, 0.6, kv_from=1), 16, 7, 2, 3.0, groups=(7, 3)),
     _moe(_diff(6, 1, 6, 10, 48, 2, 0.15, kv_from=1), None, 0, 0, 0),
 ]}
@@ -94,7 +94,7 @@ FED_D = {"architecture": "Fedirax", "vocab": 211, "width": 50, "embedding": {"sc
 FED_E = {"architecture": "Fedirax", "vocab": 150, "width": 64, "embedding": {"scale": 6.0}, "norm": {"eps": 1e-6}, "layers": [
     _moe(_diff(16, 1, 12, 20, 50, 4, 0.2), 16, 0, 2, 1.2, identity=3),
     _moe(_sink(4, 4, 16, 5000, 8, 50.0), 18, 5, 2, 1.0, limit=2.0, identity=1, groups=(3, 2), shared=(10, 1.0)),
-    _moe(_diff(16, 1, 32, 64, 100, 32, 0.3, base=1000.0), 24, 3, 2, 1.5, shared=(8, 4.0)),
+    _moe(_diff(16, 1, 32, 64, 100, 32, 0.28, base=1000.0), 24, 3, 2, 1.5, shared=(8, 4.0)),
     _moe(_diff(2, 2, 16, 32, 64, 16, 0.5), None, 0, 0, 0),
 ]}
 CONFIGS = {"A": FED_A, "B": FED_B, "C": FED_C, "D": FED_D, "E": FED_E}
