@@ -89,7 +89,9 @@ def test_bench_ops_times_every_operator():
     names = [r["op"] for r in recs]
     for want in ("embedding", "rmsnorm", "rmsnorm_float32", "rope_table", "rope_kv_write", "gemm_simt_float32",
                  "paged_attention_simt_float32", "paged_attention_tcgen05", "paged_decode_mma",
-                 "paged_decode_mma_and_merge", "argmax", "sample_top_k_top_p", "sample_temperature_only", "mma_issue"):
+                 "paged_decode_mma_and_merge", "argmax", "sample_top_k_top_p", "sample_temperature_only", "mma_issue",
+                 "head_prepare_two_maps_norm_rope_cache", "head_prepare_keys_as_values_rope_cache", "diff_combine",
+                 "moe_route_groups_identity_gate", "paged_decode_mma_window_1024_capped_sinks"):
         assert want in names, names
     assert all(r["us"] > 0 and r["MB"] > 0 for r in recs if r["op"] != "mma_issue")
     assert all(r["cycles_per_mma"] > 0 for r in recs if r["op"] == "mma_issue")
