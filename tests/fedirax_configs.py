@@ -105,6 +105,61 @@ def config(name):
     return copy.deepcopy(CONFIGS[name])
 
 
+def random_config(rng, tensor_core: bool):
+    """A configuration drawn at random: two to six layers of either kind, any head counts and sizes (with ``tensor_core``
+    the sizes the tensor-core kernels take in bfloat16), windows from 1 to 300 or none, partial rotation, layers that
+    read an earlier differential layer's cache, routers with any split into experts, identity experts, groups and a
+    shared expert, or no feed-forward."""
+    width = rng.choice([64, 128, 192]) if tensor_core else rng.choice([24, 40, 56, 72, 100])
+    layers = []
+    for _ in range(rng.randint(2, 6)):
+        kind = rng.choice(["attention", "attention_2"])
+        G = rng.choice([1, 2, 3, 4])
+        H = G * rng.choice([1, 2, 3, 4, 8])
+        if kind == "attention":
+            dim = rng.choice([64, 128]) if tensor_core else rng.choice([6, 8, 12, 20, 34, 48])
+            m = {"heads": H, "kv_heads": G, "dim": dim, "vdim": dim, "scale": dim ** -0.5 * rng.choice([1.0, 2.0])}
+            if rng.random() < 0.8:
+                m["softcap"] = rng.choice([5.0, 15.0, 40.0])
+        else:
+            dim = rng.choice([32, 64]) if tensor_core else rng.choice([4, 6, 10, 16, 24, 48])
+            vdim = 2 * dim if (tensor_core and rng.random() < 0.8) else rng.choice([6, 10, 16, 40, 64, 96])
+            m = {"heads": H, "kv_heads": G, "dim": dim, "vdim": vdim, "scale": dim ** -0.5 * rng.choice([1.0, 2.0]),
+                 "diff": rng.choice([0.1, 0.25, 0.5, 0.8])}
+            owners = [j for j, l in enumerate(layers) if l["type"] == "attention_2" and "kv_from" not in l["mixer"]]
+            if owners and rng.random() < 0.4:
+                j = rng.choice(owners)
+                o = layers[j]["mixer"]
+                m.update(heads=o["heads"], kv_heads=o["kv_heads"], dim=o["dim"], vdim=o["vdim"], kv_from=j)
+                if "rot" in o:
+                    m["rot"] = dict(o["rot"])
+        if rng.random() < 0.9:
+            m["mask"] = {"size": rng.choice([1, 2, 7, 16, 17, 31, 32, 64, 100, 129, 200, 300])}
+        if "kv_from" not in m and rng.random() < 0.9:
+            m["rot"] = {"dims": rng.choice(range(2, m["dim"] + 1, 2)), "base": rng.choice([100.0, 10000.0, 1000000.0])}
+        mlp = None
+        if rng.random() < 0.85:
+            E, ident = rng.randint(1, 12), rng.choice([0, 0, 1, 2, 4])
+            n = E + ident
+            count = rng.choice([c for c in range(1, n + 1) if n % c == 0])
+            keep = rng.randint(1, count)
+            router = {"experts": E, "top": rng.randint(1, min(4, keep * (n // count))), "scale": rng.choice([1.0, 1.7, 2.5])}
+            if ident:
+                router["identity"] = ident
+            if rng.random() < 0.8:
+                router["groups"] = {"count": count, "keep": keep}
+            ff = rng.choice([16, 32, 64]) if tensor_core else rng.choice([6, 10, 16, 28])
+            mlp = {"kind": "moe", "expert": {"ff": ff, "limit": rng.choice([0.8, 1.5, 7.0])}, "router": router}
+            if rng.random() < 0.6:
+                mlp["shared"] = {"ff": rng.choice([8, 16, 32, 96]), "limit": rng.choice([1.0, 2.0])}
+        layers.append({"type": kind, "mixer": m, "mlp": mlp})
+    cfg = {"architecture": "Fedirax", "vocab": rng.choice([97, 301, 523]), "width": width,
+           "norm": {"eps": rng.choice([1e-6, 1e-5])}, "layers": layers}
+    if rng.random() < 0.8:
+        cfg["embedding"] = {"scale": rng.choice([1.0, 2.5, 8.0])}
+    return cfg
+
+
 def tensor_shapes(cfg) -> Dict[str, tuple]:
     """Every tensor of a model of this design, by the naming rule of its checkpoints."""
     D, V = cfg["width"], cfg["vocab"]

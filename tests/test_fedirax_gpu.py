@@ -10,7 +10,7 @@ import torch
 from lightllm_b200 import Engine, EngineCore, EngineOptions, StepEntry
 from lightllm_b200.csrc import ops
 from lightllm_b200.parts import RoutedExperts
-from tests.fedirax_configs import CONFIGS, PAGE_SIZE, config, random_weights, write_model
+from tests.fedirax_configs import CONFIGS, PAGE_SIZE, config, random_config, random_weights, write_model
 from tests.plain import fedirax_plain as P
 from tests.tolerances import FEDIRAX_BF16_WORST_REL, FLOAT32_ATOL, logits_std, record
 from tests.trace_util import Trace, compare_with_plain, run_trace
@@ -533,6 +533,43 @@ def test_greedy_generation_through_the_entry_point(tmp_path, name, dtype):
     eng.core.cache.check()
     assert eng.core.cache.free_slots == 3
     eng.core.runner.check_device_errors()
+
+
+@pytest.mark.parametrize("seed", range(10))
+def test_random_configurations_through_the_engine(tmp_path, seed):
+    """Configurations drawn at random (odd sizes for even seeds, tensor-core sizes for odd ones): a prompt in portions of
+    changing size beside another request's portions, then forty tokens one by one, in both precisions against the plain
+    implementation."""
+    rng = random.Random(1000 + seed)
+    cfg = random_config(rng, tensor_core=seed % 2 == 1)
+    toks = [rng.randrange(cfg["vocab"]) for _ in range(rng.choice([90, 260, 420]))]
+    cuts = [rng.choice([2, 3, 17, 64, 131]) for _ in range(4)]
+    for dtype in ("float32", "bfloat16"):
+        w = random_weights(cfg, seed, store=DT[dtype], fixed_choice=dtype == "bfloat16")
+        d = write_model(cfg, w, str(tmp_path / f"fed_random_{seed}_{dtype}"))
+        plain = plain_logits(toks, {k: v.double() for k, v in w.items()}, cfg)
+        core = EngineCore(d, EngineOptions(dtype=dtype, max_seq_len=1024, max_batch_tokens=1024, page_size=16, num_pages=64,
+                                           max_seqs=4))
+        core.open("a")
+        core.open("b")
+        rows, at, other, i = [], 0, 0, 0
+        while at < len(toks):
+            left = len(toks) - 40 - at
+            c = max(1, min(cuts[i], left) if i < len(cuts) and left > 0 else (left if left > 0 else 1))
+            entries = [StepEntry("a", toks[at:at + c], list(range(c)))]
+            if other < len(toks) and i % 2 == 0:          # a second request beside it; its logits are not asked for
+                oc = min([1, 5, 33][i % 3], len(toks) - other)
+                entries.append(StepEntry("b", toks[other:other + oc], []))
+                other += oc
+            rows.append(core.step(entries).float().cpu()[:c])
+            at += c
+            i += 1
+        core.runner.check_device_errors()
+        d_ = torch.cat(rows).double() - plain.double()
+        err = float((d_ - d_.mean(-1, keepdim=True)).pow(2).mean(-1).sqrt().max()) / float(plain.std())
+        print(f"random configuration {seed} {dtype}: {err:.2e} of the logits' standard deviation")
+        # the largest a recorded run showed: 4e-6 (float32), 0.016 (bfloat16); a lost key or a wrong window moves it by tenths
+        assert err <= (1e-4 if dtype == "float32" else 0.05), (cfg, err)
 
 
 def test_command_lines_serve_the_design(tmp_path):
